@@ -1,0 +1,243 @@
+/*
+ * raft_b200 - C ABI of the B200 (sm_100a) dense-reduction kernels.
+ *
+ * This is the whole boundary between host code and the CUDA kernels: plain pointers, sizes,
+ * enums and a stream. The drop-in C++ headers under include/raft/linalg/ forward to these
+ * entry points when the caller's functors are ones an enum can name, and any other language
+ * can bind them directly (see the ctypes binding in raft_b200/_lib.py).
+ *
+ * The reference (RAFT 26.10) has no ABI for this path - its reductions are header-only
+ * function templates - so each entry point below names the reference template it stands for.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless stated otherwise; the caller owns all buffers;
+ *  - every call is asynchronous on `stream` and never synchronises;
+ *  - the return value is a b2r_status; B2R_ERR_CUDA means a CUDA runtime call failed and
+ *    b2r_last_cuda_error() returns its cudaError_t (per host thread);
+ *  - `workspace` may be NULL: kernels that need scratch memory then take it from the
+ *    stream-ordered allocator (cudaMallocAsync on `stream`). A caller that wants no
+ *    allocation inside the call passes b2r_*_workspace_bytes() bytes of device memory.
+ */
+#ifndef RAFT_B200_H
+#define RAFT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B2R_API
+#else
+#define B2R_API __attribute__((visibility("default")))
+#endif
+
+/* Same underlying type as cudaStream_t, without requiring the CUDA headers. */
+typedef struct CUstream_st* b2r_stream_t;
+
+typedef enum {
+  B2R_OK              = 0,
+  B2R_ERR_BAD_ARG     = 1, /* null pointer, negative size, inconsistent descriptor           */
+  B2R_ERR_UNSUPPORTED = 2, /* a dtype / operator combination the library was not built for   */
+  B2R_ERR_CUDA        = 3, /* a CUDA runtime call failed, see b2r_last_cuda_error()          */
+  B2R_ERR_TOO_LARGE   = 4  /* a size beyond a stated limit of the entry point                */
+} b2r_status;
+
+typedef enum {
+  B2R_F32 = 0,
+  B2R_F64 = 1,
+  B2R_F16 = 2,
+  B2R_I32 = 3,
+  B2R_I64 = 4,
+  B2R_I16 = 5,
+  B2R_U32 = 6,
+  /* {int32 key; V value} pairs, laid out like raft::KeyValuePair<int, V> (core/kvp.hpp:20-27) */
+  B2R_KVP_I32_F32 = 16,
+  B2R_KVP_I32_F64 = 17,
+  B2R_KVP_I32_I16 = 18,
+  B2R_KVP_I32_I32 = 19
+} b2r_dtype;
+
+typedef enum { B2R_ROW_MAJOR = 0, B2R_COL_MAJOR = 1 } b2r_layout;
+
+/* raft::Apply (core/types.hpp:16): ALONG_ROWS gives one output per row. */
+typedef enum { B2R_ALONG_ROWS = 0, B2R_ALONG_COLUMNS = 1 } b2r_apply;
+
+/* main_op(x, index along the reduced axis) - core/operators.hpp:27-107 */
+typedef enum {
+  B2R_MAIN_IDENTITY = 0, /* raft::identity_op */
+  B2R_MAIN_SQ       = 1, /* raft::sq_op       */
+  B2R_MAIN_ABS      = 2, /* raft::abs_op      */
+  B2R_MAIN_NZ       = 3, /* raft::nz_op       */
+  B2R_MAIN_TO_KVP   = 4  /* x, j -> {j, x}; required with ARGMIN / ARGMAX */
+} b2r_main_op;
+
+/* reduce_op - core/operators.hpp:109-199 */
+typedef enum {
+  B2R_REDUCE_ADD    = 0, /* raft::add_op, compensated summation */
+  B2R_REDUCE_MIN    = 1, /* raft::min_op */
+  B2R_REDUCE_MAX    = 2, /* raft::max_op */
+  B2R_REDUCE_ARGMIN = 3, /* raft::argmin_op: smaller value wins, ties -> lower key */
+  B2R_REDUCE_ARGMAX = 4  /* raft::argmax_op: larger value wins,  ties -> lower key */
+} b2r_reduce_op;
+
+/* final_op - core/operators.hpp:69-75, 300-310 */
+typedef enum {
+  B2R_FINAL_IDENTITY  = 0,
+  B2R_FINAL_SQRT      = 1, /* raft::sqrt_op                      */
+  B2R_FINAL_MUL_CONST = 2, /* raft::mul_const_op(final_scalar)   */
+  B2R_FINAL_DIV_CONST = 3, /* raft::div_const_op(final_scalar)   */
+  B2R_FINAL_ABS       = 4  /* raft::abs_op                       */
+} b2r_final_op;
+
+/* raft::linalg::NormType (linalg/norm_types.hpp:13-23) */
+typedef enum { B2R_NORM_L0 = 0, B2R_NORM_L1 = 1, B2R_NORM_L2 = 2, B2R_NORM_LINF = 3 } b2r_norm_type;
+
+typedef struct {
+  int32_t in_dtype;   /* b2r_dtype of the matrix elements                                   */
+  int32_t out_dtype;  /* b2r_dtype of the outputs (= accumulator type, as in the reference) */
+  int32_t layout;     /* b2r_layout of the matrix; it must be contiguous                    */
+  int32_t apply;      /* b2r_apply                                                          */
+  int64_t n_rows;     /* matrix extent 0                                                    */
+  int64_t n_cols;     /* matrix extent 1                                                    */
+  int32_t main_op;    /* b2r_main_op                                                        */
+  int32_t reduce_op;  /* b2r_reduce_op                                                      */
+  int32_t final_op;   /* b2r_final_op                                                       */
+  int32_t inplace;    /* non-zero: out = final(reduce(out_old, acc))                        */
+  double init;        /* initial value (floating outputs; value part of a KVP)              */
+  int64_t init_i;     /* initial value (integer outputs; integer value part of a KVP)       */
+  int64_t init_key;   /* key part of a KVP initial value                                    */
+  double final_scalar;/* operand of MUL_CONST / DIV_CONST                                   */
+} b2r_reduce_desc;
+
+/*
+ * raft::linalg::reduce - raw-pointer form linalg/reduce.cuh:55-76, mdspan form :140-180,
+ * dispatch linalg/detail/reduce.cuh:25-49 - and with it coalesced_reduction
+ * (linalg/coalesced_reduction.cuh:48-67, 104-149) and strided_reduction
+ * (linalg/strided_reduction.cuh:51-78, 115-160):
+ *     out[k] = final_op(reduce_op over the reduced axis of main_op(in[..], index))
+ * `init` must be the identity of reduce_op (for ADD it is added exactly once). As in the
+ * reference, ARGMIN / ARGMAX outputs are only available along the contiguous axis
+ * (linalg/strided_reduction.cuh:70-77).
+ */
+B2R_API int b2r_reduce(const b2r_reduce_desc* desc,
+                       void* out,
+                       const void* in,
+                       void* workspace,
+                       size_t workspace_bytes,
+                       b2r_stream_t stream);
+
+/* Scratch bytes b2r_reduce would allocate for this descriptor and input pointer (0: none). */
+B2R_API size_t b2r_reduce_workspace_bytes(const b2r_reduce_desc* desc, const void* in);
+
+/*
+ * raft::linalg::norm / rowNorm / colNorm - linalg/norm.cuh:45-59, 76-90, 112-148,
+ * linalg/detail/norm.cuh:17-61. L1 = (abs, add), L2 = (sq, add; no root unless final_op is
+ * SQRT), Linf = (abs, max); init 0, never in place. B2R_NORM_L0 returns
+ * B2R_ERR_UNSUPPORTED, as the reference throws for it.
+ */
+B2R_API int b2r_norm(int32_t norm_type,
+                     int32_t apply,
+                     int32_t layout,
+                     int32_t in_dtype,
+                     int32_t out_dtype,
+                     int64_t n_rows,
+                     int64_t n_cols,
+                     int32_t final_op,
+                     double final_scalar,
+                     void* out,
+                     const void* in,
+                     void* workspace,
+                     size_t workspace_bytes,
+                     b2r_stream_t stream);
+
+/*
+ * raft::linalg::reduce_rows_by_key - linalg/reduce_rows_by_key.cuh:52-71 (weighted),
+ * :92-116 (unweighted), impl linalg/detail/reduce_rows_by_key.cuh:353-385:
+ *     sums[keys[i]][0..ncols) += weights[i] * A[i][0..ncols)      A row-major, row stride lda
+ * `weights` may be NULL (unit weights). `reset` non-zero overwrites sums, zero accumulates
+ * into them. Keys must lie in [0, nkeys) (unchecked, as in the reference).
+ * data_dtype: B2R_F32 or B2R_F64 (sums and weights have the same type); key_dtype: B2R_I32,
+ * B2R_U32 or B2R_I64.
+ * `counts` (may be NULL) is an extension with no counterpart in the reference: int64 number of
+ * rows per key, overwritten or accumulated like sums.
+ * The reference's char scratch `d_keys_char` is not needed and has no parameter here.
+ */
+B2R_API int b2r_reduce_rows_by_key(void* sums,
+                                   int64_t* counts,
+                                   const void* A,
+                                   int64_t lda,
+                                   const void* keys,
+                                   const void* weights,
+                                   int32_t data_dtype,
+                                   int32_t key_dtype,
+                                   int64_t nrows,
+                                   int64_t ncols,
+                                   int64_t nkeys,
+                                   int32_t reset,
+                                   void* workspace,
+                                   size_t workspace_bytes,
+                                   b2r_stream_t stream);
+
+B2R_API size_t b2r_reduce_rows_by_key_workspace_bytes(
+  const void* A, int64_t lda, int32_t data_dtype, int64_t nrows, int64_t ncols, int64_t nkeys);
+
+/*
+ * raft::linalg::reduce_cols_by_key - linalg/reduce_cols_by_key.cuh:39-50, 76-102, impl
+ * linalg/detail/reduce_cols_by_key.cuh:89-138:
+ *     out[r][keys[c]] += data[r][c]        data row-major [nrows x ncols], out [nrows x nkeys]
+ * dtype: B2R_F32 or B2R_F64; key_dtype: B2R_I32, B2R_U32 or B2R_I64.
+ */
+B2R_API int b2r_reduce_cols_by_key(void* out,
+                                   const void* data,
+                                   const void* keys,
+                                   int32_t dtype,
+                                   int32_t key_dtype,
+                                   int64_t nrows,
+                                   int64_t ncols,
+                                   int64_t nkeys,
+                                   int32_t reset,
+                                   b2r_stream_t stream);
+
+/*
+ * Applies a final_op to a vector in place: v[i] = final_op(v[i]). Used by the multi-GPU
+ * host layer, which all-reduces raw per-GPU partials and applies final_op afterwards; in the
+ * reference the same step is the trailing unaryOp of linalg/detail/strided_reduction.cuh:194-195.
+ */
+B2R_API int b2r_apply_final(void* v,
+                            int32_t dtype,
+                            int64_t n,
+                            int32_t final_op,
+                            double final_scalar,
+                            b2r_stream_t stream);
+
+/*
+ * Synthetic workload generator (counter based: element i of a buffer depends only on
+ * (seed, i + first_index), so any shard of a matrix can be generated in place and a host
+ * implementation of the same hash reproduces it bit for bit). Has no counterpart in the
+ * reference, whose tests use raft::random. `kind`:
+ *   0 uniform in [lo, hi)            (f32 / f64)
+ *   1 approximately standard normal  (f32 / f64; sum of eight 16-bit uniforms, unit variance)
+ *   2 integer-valued uniform in {lo .. hi-1}   (f32 / f64 / i32 / i16 / u32 / i64)
+ */
+B2R_API int b2r_synth_fill(void* dst,
+                           int32_t dtype,
+                           int64_t n,
+                           int64_t first_index,
+                           uint64_t seed,
+                           int32_t kind,
+                           double lo,
+                           double hi,
+                           b2r_stream_t stream);
+
+B2R_API const char* b2r_status_string(int status);
+B2R_API int b2r_last_cuda_error(void);
+B2R_API const char* b2r_version(void);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* RAFT_B200_H */

@@ -1,0 +1,145 @@
+// Reduction along the strided axis of a row-major [n_rows x n_cols] matrix:
+//     out[j] = final(reduce_i main(x[i][j], i)),        i over rows.
+//
+// Replaces the reference's three-launch scheme (init map kernel, atomic strided kernel,
+// final map kernel: linalg/detail/strided_reduction.cuh:27-121, 142, 194-195) by
+//
+//  col_partial_kernel   grid (column tiles, row ranges). A CTA is TX x TY threads; a thread
+//                       owns VEC adjacent columns (one 16-byte load per row) and walks down
+//                       its rows with U loads in flight. Rows of a narrow matrix are
+//                       contiguous, so for n_cols*sizeof <= 512 B a warp's load covers
+//                       several whole rows. The TY partials per column are folded through
+//                       shared memory in a fixed order and written to
+//                       partial[row_range][n_cols] - no atomics, bit-reproducible.
+//  col_finalize_kernel  folds the row-range partials in order, applies init (once),
+//                       inplace and final_op, and writes out[j].
+// When a single row range suffices the first kernel writes the finished output itself.
+#pragma once
+
+#include "common.cuh"
+#include "ops.cuh"
+
+namespace raft_b200 {
+namespace detail {
+
+template <typename InT,
+          typename OutT,
+          typename IdxT,
+          typename MainOp,
+          typename ReduceOp,
+          typename FinalOp,
+          int VEC,
+          int U,
+          int TPB>
+__global__ void __launch_bounds__(TPB) col_partial_kernel(OutT* __restrict__ out,
+                                                         OutT* __restrict__ partial,
+                                                         const InT* __restrict__ data,
+                                                         int64_t n_rows,
+                                                         int64_t n_cols,
+                                                         int64_t ld,
+                                                         OutT init,
+                                                         bool inplace,
+                                                         MainOp main_op,
+                                                         ReduceOp reduce_op,
+                                                         FinalOp final_op,
+                                                         int TX,
+                                                         int64_t rows_per_cta)
+{
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  State* s_part = reinterpret_cast<State*>(smem_raw);  // [TY][TX*VEC]
+
+  const int TY        = TPB / TX;
+  const int tx        = threadIdx.x & (TX - 1);
+  const int ty        = threadIdx.x / TX;
+  const int64_t col0  = (int64_t(blockIdx.x) * TX + tx) * VEC;
+  const bool active   = col0 < n_cols;  // VEC divides n_cols on the vector path
+  const int64_t r_beg = int64_t(blockIdx.y) * rows_per_cta;
+  int64_t r_end       = r_beg + rows_per_cta;
+  r_end               = r_end < n_rows ? r_end : n_rows;
+  const bool direct   = gridDim.y == 1;
+
+  State st[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    if constexpr (isSum) {
+      st[e].init(OutT(0));
+    } else {
+      st[e].init(init);
+    }
+  }
+
+  if (active) {
+    const InT* cp = data + col0;
+    int64_t r     = r_beg + ty;
+    for (; r + int64_t(U - 1) * TY < r_end; r += int64_t(U) * TY) {
+      VecOf<InT, VEC> v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        v[u] = load_stream<InT, VEC>(cp + (r + int64_t(u) * TY) * ld);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          st[e].push(OutT(main_op(v[u].e[e], IdxT(r + int64_t(u) * TY))), reduce_op);
+      }
+    }
+    for (; r < r_end; r += TY) {
+      VecOf<InT, VEC> v = load_stream<InT, VEC>(cp + r * ld);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        st[e].push(OutT(main_op(v.e[e], IdxT(r))), reduce_op);
+    }
+  }
+
+  const int W = TX * VEC;
+#pragma unroll
+  for (int e = 0; e < VEC; ++e)
+    s_part[ty * W + tx * VEC + e] = st[e];
+  __syncthreads();
+
+  for (int j = threadIdx.x; j < W; j += TPB) {
+    const int64_t col = int64_t(blockIdx.x) * W + j;
+    if (col < n_cols) {
+      State r = s_part[j];
+      for (int y = 1; y < TY; ++y)
+        r.merge(s_part[y * W + j], reduce_op);
+      if (direct) {
+        if constexpr (isSum) { r.push(init, reduce_op); }
+        OutT v = r.value();
+        if (inplace) v = reduce_op(out[col], v);
+        out[col] = final_op(v);
+      } else {
+        partial[int64_t(blockIdx.y) * n_cols + col] = r.value();
+      }
+    }
+  }
+}
+
+template <typename OutT, typename ReduceOp, typename FinalOp, int TPB>
+__global__ void __launch_bounds__(TPB) col_finalize_kernel(OutT* __restrict__ out,
+                                                          const OutT* __restrict__ partial,
+                                                          int n_parts,
+                                                          int64_t n_cols,
+                                                          OutT init,
+                                                          bool inplace,
+                                                          ReduceOp reduce_op,
+                                                          FinalOp final_op)
+{
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  const int64_t col    = int64_t(blockIdx.x) * TPB + threadIdx.x;
+  if (col >= n_cols) return;
+  State st;
+  st.init(init);  // for a sum this is the single place init enters
+  (void)isSum;
+  for (int p = 0; p < n_parts; ++p)
+    st.push(partial[int64_t(p) * n_cols + col], reduce_op);
+  OutT v = st.value();
+  if (inplace) v = reduce_op(out[col], v);
+  out[col] = final_op(v);
+}
+
+}  // namespace detail
+}  // namespace raft_b200

@@ -1,0 +1,246 @@
+// Reduction along the contiguous axis: out[i] = final(reduce_j main(x[i][j], j)).
+//
+// Replaces the reference's thin / medium / thick coalesced kernels
+// (linalg/detail/coalesced_reduction-inl.cuh:48-227, 329-400, 481-533) with two kernels
+// and a shape policy:
+//
+//  row_reduce_kernel   a sub-warp of G lanes (G = 1..32, chosen from the row length) owns a
+//                      row; every lane keeps U independent 16-byte loads in flight.
+//                        kRows   mode: the U loads belong to U different rows (short rows);
+//                                      the U partials of a group are finished together by
+//                                      the transposing sub-warp reduction, which also
+//                                      spreads the outputs over lanes for a packed store.
+//                        kChunks mode: the U loads are U consecutive chunks of the SAME row
+//                                      (rows of a few KB and more, one row per group).
+//  row_split_kernel    few but very long rows: a row is cut into S segments, one CTA each;
+//                      the S partials per row go to scratch memory and a second, tiny
+//                      row_reduce_kernel pass folds them and applies init / inplace / final.
+//
+// Sums are compensated (CompensatedState); every other operator runs through
+// GenericState. main_op receives the index along the reduced axis, as in the reference.
+#pragma once
+
+#include "common.cuh"
+#include "ops.cuh"
+
+namespace raft_b200 {
+namespace detail {
+
+enum RowMode : int { kRows = 0, kChunks = 1 };
+
+template <typename OutT, typename State, bool IsSum>
+B2R_DI void init_state(State& st, const OutT& init, bool first_lane)
+{
+  if constexpr (IsSum) {
+    // the initial value enters a sum exactly once
+    st.init(first_lane ? init : OutT(0));
+  } else {
+    // any other operator: init must be its identity (or the op idempotent), as the
+    // reference requires, because every lane starts from it
+    st.init(init);
+  }
+}
+
+template <typename InT,
+          typename OutT,
+          typename IdxT,
+          typename MainOp,
+          typename ReduceOp,
+          typename FinalOp,
+          int VEC,
+          int U,
+          int MODE,
+          int TPB>
+__global__ void __launch_bounds__(TPB) row_reduce_kernel(OutT* __restrict__ out,
+                                                        const InT* __restrict__ data,
+                                                        int64_t n_rows,
+                                                        int row_len,
+                                                        int64_t ld,
+                                                        OutT init,
+                                                        bool inplace,
+                                                        MainOp main_op,
+                                                        ReduceOp reduce_op,
+                                                        FinalOp final_op,
+                                                        int G)
+{
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+
+  const int lane = threadIdx.x & 31;
+  const int lig  = lane & (G - 1);   // lane in group
+  const int grp  = lane / G;         // group in warp
+  const int gpw  = 32 / G;           // groups per warp
+  const int nvec = row_len / VEC;    // VEC divides row_len on the vector path; VEC==1 otherwise
+
+  const int64_t warps_total = int64_t(gridDim.x) * (TPB / 32);
+  const int64_t warp_global = int64_t(blockIdx.x) * (TPB / 32) + (threadIdx.x >> 5);
+
+  if constexpr (MODE == kRows) {
+    const int rows_per_batch = U * gpw;
+    const int64_t n_batches  = (n_rows + rows_per_batch - 1) / rows_per_batch;
+    for (int64_t b = warp_global; b < n_batches; b += warps_total) {
+      const int64_t row0 = b * rows_per_batch + grp;  // slot u -> row0 + u*gpw
+      State st[U];
+      const InT* rp[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        init_state<OutT, State, isSum>(st[u], init, lig == 0);
+        int64_t r = row0 + int64_t(u) * gpw;
+        r         = r < n_rows ? r : n_rows - 1;  // clamp: duplicate work instead of divergence
+        rp[u]     = data + r * ld;
+      }
+      for (int c = lig; c < nvec; c += G) {
+        VecOf<InT, VEC> v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          v[u] = load_stream<InT, VEC>(rp[u] + int64_t(c) * VEC);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            st[u].push(OutT(main_op(v[u].e[e], IdxT(c * VEC + e))), reduce_op);
+        }
+      }
+      subwarp_transpose_reduce<U>(st, lig, G, reduce_op);
+      const SubwarpLayout lay = subwarp_layout<U>(lig, G);
+      if (lay.writer) {
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          if (i < lay.n_final) {
+            const int slot  = lay.prefix * lay.n_final + i;
+            const int64_t r = row0 + int64_t(slot) * gpw;
+            if (r < n_rows) {
+              OutT v = st[i].value();
+              if (inplace) v = reduce_op(out[r], v);
+              out[r] = final_op(v);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // kChunks: one row per group, U chunks of it in flight per lane.
+    const int64_t n_batches = (n_rows + gpw - 1) / gpw;
+    for (int64_t b = warp_global; b < n_batches; b += warps_total) {
+      const int64_t row = b * gpw + grp;
+      const int64_t rc  = row < n_rows ? row : n_rows - 1;
+      const InT* rp     = data + rc * ld;
+      State st[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        init_state<OutT, State, isSum>(st[u], init, lig == 0 && u == 0);
+      int c = lig;
+      for (; c + (U - 1) * G < nvec; c += U * G) {
+        VecOf<InT, VEC> v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          v[u] = load_stream<InT, VEC>(rp + int64_t(c + u * G) * VEC);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            st[u].push(OutT(main_op(v[u].e[e], IdxT((c + u * G) * VEC + e))), reduce_op);
+        }
+      }
+      for (; c < nvec; c += G) {
+        VecOf<InT, VEC> v = load_stream<InT, VEC>(rp + int64_t(c) * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          st[0].push(OutT(main_op(v.e[e], IdxT(c * VEC + e))), reduce_op);
+      }
+#pragma unroll
+      for (int u = 1; u < U; ++u)
+        st[0].merge(st[u], reduce_op);
+      for (int off = G >> 1; off > 0; off >>= 1) {
+        State got = shfl_xor_any(st[0], off);
+        st[0].merge(got, reduce_op);
+      }
+      if (lig == 0 && row < n_rows) {
+        OutT v = st[0].value();
+        if (inplace) v = reduce_op(out[row], v);
+        out[row] = final_op(v);
+      }
+    }
+  }
+}
+
+// One CTA per (segment, row). Writes either the finished output (n_seg == 1) or the
+// partial of its segment to partial[row * n_seg + seg].
+template <typename InT,
+          typename OutT,
+          typename IdxT,
+          typename MainOp,
+          typename ReduceOp,
+          typename FinalOp,
+          int VEC,
+          int U,
+          int TPB>
+__global__ void __launch_bounds__(TPB) row_split_kernel(OutT* __restrict__ out,
+                                                       OutT* __restrict__ partial,
+                                                       const InT* __restrict__ data,
+                                                       int64_t n_rows,
+                                                       int64_t row_len,
+                                                       int64_t ld,
+                                                       OutT init,
+                                                       bool inplace,
+                                                       MainOp main_op,
+                                                       ReduceOp reduce_op,
+                                                       FinalOp final_op,
+                                                       int64_t seg_vecs)
+{
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  __shared__ State s_warp[TPB / 32];
+
+  const int n_seg    = gridDim.x;
+  const int seg      = blockIdx.x;
+  const int64_t nvec = row_len / VEC;
+  const int64_t v0   = int64_t(seg) * seg_vecs;
+  int64_t v1         = v0 + seg_vecs;
+  v1                 = v1 < nvec ? v1 : nvec;
+  const bool direct  = n_seg == 1;
+
+  for (int64_t row = blockIdx.y; row < n_rows; row += gridDim.y) {
+    const InT* rp = data + row * ld;
+    State st[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      init_state<OutT, State, isSum>(st[u], init, direct && threadIdx.x == 0 && u == 0);
+    int64_t c = v0 + threadIdx.x;
+    for (; c + int64_t(U - 1) * TPB < v1; c += int64_t(U) * TPB) {
+      VecOf<InT, VEC> v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        v[u] = load_stream<InT, VEC>(rp + (c + int64_t(u) * TPB) * VEC);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          st[u].push(OutT(main_op(v[u].e[e], IdxT((c + int64_t(u) * TPB) * VEC + e))), reduce_op);
+      }
+    }
+    for (; c < v1; c += TPB) {
+      VecOf<InT, VEC> v = load_stream<InT, VEC>(rp + c * VEC);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        st[0].push(OutT(main_op(v.e[e], IdxT(c * VEC + e))), reduce_op);
+    }
+#pragma unroll
+    for (int u = 1; u < U; ++u)
+      st[0].merge(st[u], reduce_op);
+    State r = block_merge(st[0], reduce_op, s_warp);
+    if (threadIdx.x == 0) {
+      OutT v = r.value();
+      if (direct) {
+        if (inplace) v = reduce_op(out[row], v);
+        out[row] = final_op(v);
+      } else {
+        partial[row * n_seg + seg] = v;
+      }
+    }
+    __syncthreads();  // s_warp is reused by the next row
+  }
+}
+
+}  // namespace detail
+}  // namespace raft_b200

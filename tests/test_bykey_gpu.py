@@ -1,0 +1,104 @@
+"""Parity of b2r_reduce_rows_by_key / b2r_reduce_cols_by_key with the fp64 oracle over the
+reference's test shapes (cpp/tests/linalg/reduce_rows_by_key.cu:164-263,
+cpp/tests/linalg/reduce_cols_by_key.cu:107-126)."""
+import numpy as np
+import pytest
+import torch
+
+from raft_b200 import linalg
+from util import device_synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("nobs,cols,nkeys,dt,tol", [
+    (128, 32, 6, np.float32, 1e-6),
+    (128, 32, 3, np.float32, 1e-6),
+    (512, 1024, 40, np.float64, 1e-9),
+    (100000, 37, 32, np.float32, 1e-5),
+    (100000, 37, 2048, np.float32, 1e-5),
+    (20000, 128, 1024, np.float32, 1e-5),
+    (5000, 4, 7, np.float32, 1e-5),
+    (3000, 130, 300, np.float64, 1e-9),
+])
+@pytest.mark.parametrize("weighted", [False, True])
+@pytest.mark.parametrize("key_dt", [np.int32, np.int64])
+def test_rows_by_key_grid(cuda, oracle, nobs, cols, nkeys, dt, tol, weighted, key_dt):
+    A, hA = device_synth((nobs, cols), dt, 1234, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((nobs,), key_dt, 4321, "int", 0, nkeys, cuda)
+    w, hw = device_synth((nobs,), dt, 77, "uniform", 0, 2, cuda) if weighted else (None, None)
+    counts = torch.empty(nkeys, dtype=torch.int64, device=cuda)
+    sums = linalg.reduce_rows_by_key(A, keys, nkeys, d_weights=w, counts=counts)
+    esum, ecnt = oracle.rows_by_key(hA, hk, nkeys, weights=hw)
+    oracle.assert_approx(esum, sums.cpu().numpy(), tol, "reset")
+    assert np.array_equal(counts.cpu().numpy(), ecnt)  # counts are exact
+    # accumulate a second time without reset (reset_sums=false of the reference)
+    linalg.reduce_rows_by_key(A, keys, nkeys, d_sums=sums, d_weights=w, reset_sums=False, counts=counts)
+    oracle.assert_approx(2 * esum, sums.cpu().numpy(), 2 * tol, "accumulate")
+    assert np.array_equal(counts.cpu().numpy(), 2 * ecnt)
+
+
+def test_rows_by_key_lda_and_workspace(cuda, oracle):
+    nobs, cols, lda, nkeys = 7001, 48, 64, 200
+    full, hfull = device_synth((nobs, lda), np.float32, 9, "normal", 0, 1, cuda)
+    keys, hk = device_synth((nobs,), np.int32, 10, "int", 0, nkeys, cuda)
+    A = full[:, :cols]  # row stride 64, 48 used columns
+    sums = linalg.reduce_rows_by_key(A, keys, nkeys)
+    esum, _ = oracle.rows_by_key(np.ascontiguousarray(hfull[:, :cols]), hk, nkeys)
+    oracle.assert_approx(esum, sums.cpu().numpy(), 1e-5)
+    need = linalg.reduce_rows_by_key_workspace_bytes(A, nkeys, lda=lda)
+    assert need > 0
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda)
+    sums2 = linalg.reduce_rows_by_key(A, keys, nkeys, workspace=ws)
+    oracle.assert_approx(esum, sums2.cpu().numpy(), 1e-5)
+
+
+def test_rows_by_key_skewed_and_missing_keys(cuda, oracle):
+    nobs, cols, nkeys = 50000, 64, 500
+    A, hA = device_synth((nobs, cols), np.float32, 21, "normal", 0, 1, cuda)
+    hk = np.zeros(nobs, dtype=np.int32)
+    hk[::7] = 499
+    hk[1::1000] = 250  # most keys never occur, one key dominates
+    keys = torch.from_numpy(hk).to(cuda)
+    counts = torch.empty(nkeys, dtype=torch.int64, device=cuda)
+    sums = linalg.reduce_rows_by_key(A, keys, nkeys, counts=counts)
+    esum, ecnt = oracle.rows_by_key(hA, hk, nkeys)
+    oracle.assert_approx(esum, sums.cpu().numpy(), 1e-5)
+    assert np.array_equal(counts.cpu().numpy(), ecnt)
+
+
+def test_rows_by_key_empty(cuda):
+    A = torch.empty((0, 16), dtype=torch.float32, device=cuda)
+    keys = torch.empty((0,), dtype=torch.int32, device=cuda)
+    sums = torch.full((5, 16), 3.0, device=cuda)
+    linalg.reduce_rows_by_key(A, keys, 5, d_sums=sums, reset_sums=False)
+    assert torch.all(sums == 3.0)
+    linalg.reduce_rows_by_key(A, keys, 5, d_sums=sums, reset_sums=True)
+    assert torch.all(sums == 0.0)
+
+
+# cpp/tests/linalg/reduce_cols_by_key.cu:107-126 (a representative subset of the 60-case grid,
+# every extreme included)
+@pytest.mark.parametrize("rows,cols,nkeys", [(1, 1234, 7), (1, 101010, 2022), (9, 9999, 42), (63, 1234, 515),
+                                             (63, 101010, 127), (1024, 1234, 7), (1024, 9999, 2022),
+                                             (1024, 1234, 127), (9, 101010, 7), (3000, 300, 60000)])
+@pytest.mark.parametrize("dt,tol", [(np.float32, 1e-3), (np.float64, 1e-6)])
+def test_cols_by_key_grid(cuda, oracle, rows, cols, nkeys, dt, tol):
+    data, hd = device_synth((rows, cols), dt, 1234, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((cols,), np.int32, 55, "int", 0, nkeys, cuda)
+    out = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys)
+    exp = oracle.cols_by_key(hd, hk, nkeys)
+    oracle.assert_approx(exp, out.cpu().numpy(), tol, "reset")
+    linalg.reduce_cols_by_key(data, keys, out=out, reset_sums=False)
+    oracle.assert_approx(2 * exp, out.cpu().numpy(), 2 * tol, "accumulate")
+
+
+def test_cols_by_key_shape_errors(cuda):
+    data = torch.ones((4, 6), device=cuda)
+    keys = torch.zeros(6, dtype=torch.int32, device=cuda)
+    with pytest.raises(ValueError):
+        linalg.reduce_cols_by_key(data, keys, out=torch.zeros((3, 2), device=cuda))
+    with pytest.raises(ValueError):
+        linalg.reduce_cols_by_key(data, keys[:5], nkeys=2)
+    with pytest.raises(ValueError):
+        linalg.reduce_cols_by_key(data, keys, out=torch.zeros((4, 2), device=cuda), nkeys=3)
