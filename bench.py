@@ -27,7 +27,6 @@ that library is absent it times the OpenMP host port of the path instead.
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -65,7 +64,7 @@ def algorithmic_bytes(name):
 
 
 def launches_per_step(name):
-    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 2}[name]
+    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 3}[name]
 
 
 class Workload:
@@ -190,51 +189,68 @@ def time_steps(w, steps, warmup, flush):
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons through NVML (read-only queries) every few
+    milliseconds while the timed region runs."""
 
-    def __init__(self, index):
+    def __init__(self, index, period_s=0.002):
         super().__init__(daemon=True)
-        self.index, self.samples, self._stop_evt, self.proc = index, [], threading.Event(), None
+        self.index, self.period, self.samples, self._stop_evt = index, period_s, [], threading.Event()
+        self.max_mhz, self.ok = None, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def _sample(self):
+        nv = self.nv
+        mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+        try:
+            reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+        except Exception:
+            reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        self.samples.append((mhz, reasons))
 
     def run(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            for line in self.proc.stdout:
-                self.samples.append(line.strip())
-                if self._stop_evt.is_set():
-                    break
-        except Exception:
-            pass
+        if not self.ok:
+            return
+        while not self._stop_evt.is_set():
+            try:
+                self._sample()
+            except Exception:
+                break
+            time.sleep(self.period)
 
     def stop(self):
+        if self.ok:
+            try:
+                self._sample()  # at least one sample taken before the closing synchronize returns
+            except Exception:
+                pass
         self._stop_evt.set()
-        if self.proc is not None:
-            self.proc.terminate()  # the exact child started above
-        self.join(timeout=2)
+        if self.is_alive():
+            self.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], 0.0, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            f = [x.strip() for x in s.split(",")]
-            if len(f) < 8:
-                continue
-            try:
-                sm.append(float(f[0]))
-                mx = max(mx, float(f[1]))
-            except ValueError:
-                continue
-            for nm, v in zip(names, f[4:8]):
-                if v.lower().startswith("active"):
-                    reasons.add(nm)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        nv = self.nv
+        bits = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        mhz = sorted(m for m, _ in self.samples)
+        seen = set()
+        for _, r in self.samples:
+            for name, bit in bits.items():
+                if r & bit:
+                    seen.add(name)
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(seen),
+                "samples": len(mhz)}
 
 
 def cpu_baseline(name, budget_rows=None):
@@ -336,12 +352,15 @@ def e2e_measure(w, steps):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")
     ap.add_argument("--no-configs", action="store_true", help="skip the per-config table (N = 1 only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="override the row count of the workload (small cases for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -349,6 +368,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     name = args.workload
+    if args.rows > 0:
+        r0, c0, d0 = WORKLOADS[name]
+        WORKLOADS[name] = (args.rows, c0, d0 + f" [rows overridden: {args.rows}]")
     rows, cols, desc = WORKLOADS[name]
 
     # ---- reference arm without its library: the OpenMP host port, rank 0 only ----------------
@@ -395,6 +417,7 @@ def main():
     barrier()
     if sampler:
         sampler.start()
+        time.sleep(0.01)  # let the sampler take its first reading before the launches start
     t_wall0 = time.perf_counter()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     per = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
@@ -422,7 +445,7 @@ def main():
 
     # ---- end to end through host buffers -------------------------------------------------------
     e2e_steps = max(2, min(args.steps, 10))
-    e_ms, h2d, d2h = e2e_measure(w, e2e_steps)
+    e_ms, h2d, d2h = e2e_measure(w, e2e_steps) if not args.no_e2e else (float("nan"), 0, 0)
     te = torch.tensor([e_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)

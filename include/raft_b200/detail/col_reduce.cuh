@@ -31,8 +31,8 @@ template <typename InT,
           int VEC,
           int U,
           int TPB>
-__global__ void __launch_bounds__(TPB) col_partial_kernel(OutT* __restrict__ out,
-                                                         OutT* __restrict__ partial,
+__global__ void __launch_bounds__(TPB, 4) col_partial_kernel(OutT* __restrict__ out,
+                                                         typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
                                                          const InT* __restrict__ data,
                                                          int64_t n_rows,
                                                          int64_t n_cols,
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(TPB) col_partial_kernel(OutT* __restrict__ out
         if (inplace) v = reduce_op(out[col], v);
         out[col] = final_op(v);
       } else {
-        partial[int64_t(blockIdx.y) * n_cols + col] = r.value();
+        partial[int64_t(blockIdx.y) * n_cols + col] = r.carry();
       }
     }
   }
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(TPB) col_partial_kernel(OutT* __restrict__ out
 
 template <typename OutT, typename ReduceOp, typename FinalOp, int TPB>
 __global__ void __launch_bounds__(TPB) col_finalize_kernel(OutT* __restrict__ out,
-                                                          const OutT* __restrict__ partial,
+                                                          const typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
                                                           int n_parts,
                                                           int64_t n_cols,
                                                           OutT init,
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(TPB) col_finalize_kernel(OutT* __restrict__ ou
   st.init(init);  // for a sum this is the single place init enters
   (void)isSum;
   for (int p = 0; p < n_parts; ++p)
-    st.push(partial[int64_t(p) * n_cols + col], reduce_op);
+    st.push_carry(partial[int64_t(p) * n_cols + col], reduce_op);
   OutT v = st.value();
   if (inplace) v = reduce_op(out[col], v);
   out[col] = final_op(v);

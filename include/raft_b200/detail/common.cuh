@@ -139,7 +139,8 @@ B2R_DI T shfl_idx_any(const T& v, int src_lane)
 // Accumulator states.
 //
 //  * GenericState<Acc, Op>      acc = op(acc, x)            any commutative+associative op
-//  * CompensatedState<Acc>      Kahan-Babuska-Neumaier running sum: (s, c) with the rounding
+//  * WideSumState               fp32 values summed in an fp64 accumulator (all float sums)
+//  * CompensatedState<Acc>      (double sums) Kahan-Babuska-Neumaier running sum: (s, c) with the rounding
 //                               error of every addition collected in c; value() = s + c.
 //                               The reference compensates its add_op reductions the same way
 //                               (linalg/detail/coalesced_reduction-inl.cuh:36-46), but drops
@@ -163,17 +164,23 @@ B2R_DI double abs_any<double>(double v)
   return fabs(v);
 }
 
+// Every state also names `carry_t`, the type in which a partial result travels between two
+// kernels of one reduction (scratch memory), with carry() / push_carry().
 template <typename Acc, typename Op>
 struct GenericState {
+  using carry_t = Acc;
   Acc v;
   B2R_DI void init(const Acc& i) { v = i; }
   B2R_DI void push(const Acc& x, const Op& op) { v = op(v, x); }
   B2R_DI void merge(const GenericState& o, const Op& op) { v = op(v, o.v); }
   B2R_DI Acc value() const { return v; }
+  B2R_DI carry_t carry() const { return v; }
+  B2R_DI void push_carry(const carry_t& x, const Op& op) { v = op(v, x); }
 };
 
 template <typename Acc>
 struct CompensatedState {
+  using carry_t = Acc;
   Acc s;
   Acc c;
   B2R_DI void init(const Acc& i)
@@ -198,6 +205,39 @@ struct CompensatedState {
     c += o.c;
   }
   B2R_DI Acc value() const { return s + c; }
+  B2R_DI carry_t carry() const { return s + c; }
+  template <typename Op>
+  B2R_DI void push_carry(const carry_t& x, const Op& op)
+  {
+    push(x, op);
+  }
+};
+
+// Sum of fp32 values carried in fp64: one conversion and one double add per element instead of
+// the eight fp32 operations of the compensated update, and more accurate (53-bit running sum;
+// the result is rounded to fp32 once, at the very end). B200 runs fp64 adds at half the fp32
+// rate, which this path - a few elements per clock per SM - does not come near.
+struct WideSumState {
+  using carry_t = double;
+  double s;
+  B2R_DI void init(const float& i) { s = double(i); }
+  template <typename Op>
+  B2R_DI void push(const float& x, const Op&)
+  {
+    s += double(x);
+  }
+  template <typename Op>
+  B2R_DI void merge(const WideSumState& o, const Op&)
+  {
+    s += o.s;
+  }
+  B2R_DI float value() const { return float(s); }
+  B2R_DI carry_t carry() const { return s; }
+  template <typename Op>
+  B2R_DI void push_carry(const carry_t& x, const Op&)
+  {
+    s += x;
+  }
 };
 
 // Tag that operator types carry (or are mapped to) when the reduction is a plain sum and
@@ -205,10 +245,16 @@ struct CompensatedState {
 template <typename Op>
 struct is_sum_op : std::false_type {};
 
+// float sums -> WideSumState, double sums -> CompensatedState<double>, anything else generic
+template <typename Acc>
+struct sum_state {
+  using type = typename std::conditional<std::is_same<Acc, float>::value, WideSumState, CompensatedState<Acc>>::type;
+};
+
 template <typename Acc, typename Op>
 struct state_for {
   using type = typename std::conditional<is_sum_op<Op>::value && std::is_floating_point<Acc>::value,
-                                         CompensatedState<Acc>,
+                                         typename sum_state<Acc>::type,
                                          GenericState<Acc, Op>>::type;
 };
 

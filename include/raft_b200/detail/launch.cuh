@@ -69,11 +69,13 @@ inline int sm_count()
 // Launch-shape knobs. The defaults are the measured best on B200; the environment
 // variables exist so that a benchmark can sweep them without rebuilding.
 struct Tuning {
-  int row_batches_per_warp = 1;   // B2R_ROW_BPW   row batches a warp works through
+  int row_ctas_per_sm      = 0;   // B2R_ROW_CPS   row-kernel CTAs per SM (0: as many as are resident)
   int row_chunk_threshold  = 4;   // B2R_ROW_CHUNK rows with >= this many vectors per lane use kChunks
-  int col_ctas_per_sm      = 16;  // B2R_COL_CPS   column-partial CTAs launched per SM
+  int col_ctas_per_sm      = 4;   // B2R_COL_CPS   column-partial CTAs per SM (one resident wave)
   int split_ctas_per_sm    = 4;   // B2R_SPLIT_CPS
-  int key_block_rows       = 4096;  // B2R_KEY_BLOCK rows per key staging block (rows-by-key)
+  int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
+  int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
+  int key_algo             = 0;     // B2R_KEY_ALGO   0: auto, 1: shared-memory table, 2: sort then stream
 };
 
 inline int env_int(const char* name, int dflt)
@@ -88,12 +90,28 @@ inline Tuning tuning()
 {
   // read on every call (five getenv look-ups) so that a benchmark can sweep within one process
   Tuning x;
-  x.row_batches_per_warp = env_int("B2R_ROW_BPW", x.row_batches_per_warp);
+  x.row_ctas_per_sm      = env_int("B2R_ROW_CPS", x.row_ctas_per_sm);
   x.row_chunk_threshold  = env_int("B2R_ROW_CHUNK", x.row_chunk_threshold);
   x.col_ctas_per_sm      = env_int("B2R_COL_CPS", x.col_ctas_per_sm);
   x.split_ctas_per_sm    = env_int("B2R_SPLIT_CPS", x.split_ctas_per_sm);
   x.key_block_rows       = env_int("B2R_KEY_BLOCK", x.key_block_rows);
+  x.key_window_rows      = env_int("B2R_KEY_WINDOW", x.key_window_rows);
+  x.key_algo             = env_int("B2R_KEY_ALGO", x.key_algo);
   return x;
+}
+
+// Resident CTAs per SM of a kernel: the reductions launch exactly one resident wave and loop
+// inside the kernel (measured on B200: one wave of long-lived CTAs reads ~15 % faster than
+// many short ones).
+template <typename Kernel>
+inline int resident_ctas(Kernel kern, int tpb, size_t smem)
+{
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, tpb, smem) != cudaSuccess || n < 1) {
+    (void)cudaGetLastError();
+    n = 1;
+  }
+  return n;
 }
 
 template <typename T>
@@ -107,7 +125,7 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // ---------------------------------------------------------------------------------------
 // Row-wise (contiguous axis) reduction.
 // ---------------------------------------------------------------------------------------
-template <typename OutT>
+template <typename CarryT>
 inline size_t row_reduce_scratch_bytes(int64_t n_rows, int64_t row_len, size_t in_size, int* n_seg_out)
 {
   // Split rows only when there are too few rows to occupy the machine with one warp per
@@ -122,7 +140,7 @@ inline size_t row_reduce_scratch_bytes(int64_t n_rows, int64_t row_len, size_t i
     if (n_seg < 1) n_seg = 1;
   }
   if (n_seg_out) *n_seg_out = n_seg;
-  return n_seg > 1 ? align_up(size_t(n_rows) * n_seg * sizeof(OutT), 256) : 0;
+  return n_seg > 1 ? align_up(size_t(n_rows) * n_seg * sizeof(CarryT), 256) : 0;
 }
 
 template <typename InT,
@@ -151,13 +169,14 @@ cudaError_t launch_row_reduce(OutT* out,
 
   const bool vec_ok = V16 > 1 && row_len % V16 == 0 && ld % V16 == 0 && aligned16(data);
   int n_seg         = 1;
-  const size_t need = row_reduce_scratch_bytes<OutT>(n_rows, row_len, sizeof(InT), &n_seg);
+  using CarryT      = typename state_for<OutT, ReduceOp>::type::carry_t;
+  const size_t need = row_reduce_scratch_bytes<CarryT>(n_rows, row_len, sizeof(InT), &n_seg);
 
   if (n_seg > 1 || row_len > int64_t(0x7fffffff)) {
     // long rows: CTA per (segment, row), then fold the segment partials
     Scratch scratch(ws, need, stream);
     if (scratch.error() != cudaSuccess) return scratch.error();
-    OutT* partial         = static_cast<OutT*>(scratch.get());
+    CarryT* partial       = static_cast<CarryT*>(scratch.get());
     const int vec         = vec_ok ? V16 : 1;
     const int64_t nvec    = row_len / vec;
     int64_t seg_vecs      = ceil_div<int64_t>(nvec, n_seg);
@@ -176,12 +195,9 @@ cudaError_t launch_row_reduce(OutT* out,
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || n_seg == 1) return e;
-    const int G             = int(next_pow2(unsigned(n_seg)) > 32u ? 32u : next_pow2(unsigned(n_seg)));
-    const int64_t n_batches = ceil_div<int64_t>(n_rows, int64_t(U) * (32 / G));
-    const int64_t ctas      = ceil_div<int64_t>(n_batches, TPB / 32);
-    row_reduce_kernel<OutT, OutT, IdxT, op::Identity, ReduceOp, FinalOp, 1, U, kRows, TPB>
-      <<<unsigned(ctas), TPB, 0, stream>>>(
-        out, partial, n_rows, n_seg, n_seg, init, inplace, op::Identity{}, reduce_op, final_op, G);
+    row_finalize_kernel<OutT, ReduceOp, FinalOp, TPB>
+      <<<unsigned(ceil_div<int64_t>(n_rows, TPB / 32)), TPB, 0, stream>>>(
+        out, partial, n_rows, n_seg, init, inplace, reduce_op, final_op);
     return cudaGetLastError();
   }
 
@@ -193,15 +209,23 @@ cudaError_t launch_row_reduce(OutT* out,
   const int gpw        = 32 / G;
   const int64_t per_b  = chunks ? gpw : int64_t(U) * gpw;
   const int64_t n_b    = ceil_div<int64_t>(n_rows, per_b);
-  int64_t ctas         = ceil_div<int64_t>(n_b, int64_t(TPB / 32) * tuning().row_batches_per_warp);
-  const int64_t max_gx = 0x7fffffff;
-  if (ctas > max_gx) ctas = max_gx;
-  const int rl = int(row_len);
+  const int rl         = int(row_len);
+  const int cps_knob   = tuning().row_ctas_per_sm;
+  const int sms        = sm_count();
 
 #define B2R_LAUNCH_ROW(VEC_, MODE_)                                                              \
-  row_reduce_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, U, MODE_, TPB>             \
-    <<<unsigned(ctas), TPB, 0, stream>>>(                                                        \
-      out, data, n_rows, rl, ld, init, inplace, main_op, reduce_op, final_op, G)
+  do {                                                                                           \
+    auto kern      = row_reduce_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, U, MODE_, TPB>; \
+    static int occ = resident_ctas(kern, TPB, 0);                                                \
+    int64_t ctas   = int64_t(sms) * (cps_knob > 0 ? cps_knob : occ);                             \
+    const int64_t most = ceil_div<int64_t>(n_b, TPB / 32);                                       \
+    if (ctas > most) ctas = most;                                                                \
+    int64_t bpc = ceil_div<int64_t>(n_b, ctas);                                                  \
+    bpc         = ceil_div<int64_t>(bpc, TPB / 32) * (TPB / 32);                                 \
+    ctas        = ceil_div<int64_t>(n_b, bpc);                                                   \
+    kern<<<unsigned(ctas), TPB, 0, stream>>>(                                                    \
+      out, data, n_rows, rl, ld, init, inplace, main_op, reduce_op, final_op, G, bpc);           \
+  } while (0)
   if (vec_ok) {
     if (chunks) {
       B2R_LAUNCH_ROW(V16, kChunks);
@@ -260,7 +284,7 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
   p.grid_y       = unsigned(gy);
   p.rows_per_cta = rpc;
   p.smem         = size_t(TPB) * p.vec * sizeof(State);
-  p.scratch      = gy > 1 ? align_up(size_t(gy) * size_t(n_cols) * sizeof(OutT), 256) : 0;
+  p.scratch      = gy > 1 ? align_up(size_t(gy) * size_t(n_cols) * sizeof(typename State::carry_t), 256) : 0;
   return p;
 }
 
@@ -301,7 +325,8 @@ cudaError_t launch_col_reduce(OutT* out,
   const ColPlan p = plan_col_reduce<InT, OutT, State>(data, n_rows > 0 ? n_rows : 1, n_cols, ld);
   Scratch scratch(ws, p.scratch, stream);
   if (scratch.error() != cudaSuccess) return scratch.error();
-  OutT* partial = static_cast<OutT*>(scratch.get());
+  using CarryT    = typename State::carry_t;
+  CarryT* partial = static_cast<CarryT*>(scratch.get());
   const dim3 grid(p.grid_x, p.grid_y);
 
   if (p.vec > 1) {

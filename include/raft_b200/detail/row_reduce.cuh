@@ -51,7 +51,7 @@ template <typename InT,
           int U,
           int MODE,
           int TPB>
-__global__ void __launch_bounds__(TPB) row_reduce_kernel(OutT* __restrict__ out,
+__global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_kernel(OutT* __restrict__ out,
                                                         const InT* __restrict__ data,
                                                         int64_t n_rows,
                                                         int row_len,
@@ -61,7 +61,8 @@ __global__ void __launch_bounds__(TPB) row_reduce_kernel(OutT* __restrict__ out,
                                                         MainOp main_op,
                                                         ReduceOp reduce_op,
                                                         FinalOp final_op,
-                                                        int G)
+                                                        int G,
+                                                        int64_t batches_per_cta)
 {
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
@@ -72,33 +73,55 @@ __global__ void __launch_bounds__(TPB) row_reduce_kernel(OutT* __restrict__ out,
   const int gpw  = 32 / G;           // groups per warp
   const int nvec = row_len / VEC;    // VEC divides row_len on the vector path; VEC==1 otherwise
 
-  const int64_t warps_total = int64_t(gridDim.x) * (TPB / 32);
-  const int64_t warp_global = int64_t(blockIdx.x) * (TPB / 32) + (threadIdx.x >> 5);
+  // A CTA owns a contiguous range of row batches (so that it streams one contiguous piece of
+  // the matrix); its warps interleave inside the range.
+  constexpr int64_t warps_total = TPB / 32;
+  const int64_t cta_first       = int64_t(blockIdx.x) * batches_per_cta;
+  const int64_t warp_global     = cta_first + (threadIdx.x >> 5);
 
   if constexpr (MODE == kRows) {
     const int rows_per_batch = U * gpw;
-    const int64_t n_batches  = (n_rows + rows_per_batch - 1) / rows_per_batch;
+    int64_t n_batches        = (n_rows + rows_per_batch - 1) / rows_per_batch;
+    n_batches                = n_batches < cta_first + batches_per_cta ? n_batches : cta_first + batches_per_cta;
     for (int64_t b = warp_global; b < n_batches; b += warps_total) {
       const int64_t row0 = b * rows_per_batch + grp;  // slot u -> row0 + u*gpw
+      // slots of this group that are real rows; the others re-read the last real row (their
+      // results are never stored), which keeps the load pattern uniform
+      const int64_t left = n_rows - row0;
+      int valid          = left <= 0 ? 0 : int((left + gpw - 1) / gpw < U ? (left + gpw - 1) / gpw : U);
+      const InT* base    = data + (valid > 0 ? row0 : n_rows - 1) * ld;
+      const int64_t step = valid > 0 ? int64_t(gpw) * ld : 0;
       State st[U];
-      const InT* rp[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
+      for (int u = 0; u < U; ++u)
         init_state<OutT, State, isSum>(st[u], init, lig == 0);
-        int64_t r = row0 + int64_t(u) * gpw;
-        r         = r < n_rows ? r : n_rows - 1;  // clamp: duplicate work instead of divergence
-        rp[u]     = data + r * ld;
-      }
-      for (int c = lig; c < nvec; c += G) {
-        VecOf<InT, VEC> v[U];
+      if (valid == U) {
+        for (int c = lig; c < nvec; c += G) {
+          VecOf<InT, VEC> v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-          v[u] = load_stream<InT, VEC>(rp[u] + int64_t(c) * VEC);
+          for (int u = 0; u < U; ++u)
+            v[u] = load_stream<InT, VEC>(base + u * step + int64_t(c) * VEC);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
+          for (int u = 0; u < U; ++u) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e)
-            st[u].push(OutT(main_op(v[u].e[e], IdxT(c * VEC + e))), reduce_op);
+            for (int e = 0; e < VEC; ++e)
+              st[u].push(OutT(main_op(v[u].e[e], IdxT(c * VEC + e))), reduce_op);
+          }
+        }
+      } else {
+        for (int c = lig; c < nvec; c += G) {
+          VecOf<InT, VEC> v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int uu = u < valid ? u : (valid > 0 ? valid - 1 : 0);
+            v[u]         = load_stream<InT, VEC>(base + uu * step + int64_t(c) * VEC);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              st[u].push(OutT(main_op(v[u].e[e], IdxT(c * VEC + e))), reduce_op);
+          }
         }
       }
       subwarp_transpose_reduce<U>(st, lig, G, reduce_op);
@@ -120,7 +143,8 @@ __global__ void __launch_bounds__(TPB) row_reduce_kernel(OutT* __restrict__ out,
     }
   } else {
     // kChunks: one row per group, U chunks of it in flight per lane.
-    const int64_t n_batches = (n_rows + gpw - 1) / gpw;
+    int64_t n_batches = (n_rows + gpw - 1) / gpw;
+    n_batches         = n_batches < cta_first + batches_per_cta ? n_batches : cta_first + batches_per_cta;
     for (int64_t b = warp_global; b < n_batches; b += warps_total) {
       const int64_t row = b * gpw + grp;
       const int64_t rc  = row < n_rows ? row : n_rows - 1;
@@ -176,7 +200,7 @@ template <typename InT,
           int U,
           int TPB>
 __global__ void __launch_bounds__(TPB) row_split_kernel(OutT* __restrict__ out,
-                                                       OutT* __restrict__ partial,
+                                                       typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
                                                        const InT* __restrict__ data,
                                                        int64_t n_rows,
                                                        int64_t row_len,
@@ -230,15 +254,48 @@ __global__ void __launch_bounds__(TPB) row_split_kernel(OutT* __restrict__ out,
       st[0].merge(st[u], reduce_op);
     State r = block_merge(st[0], reduce_op, s_warp);
     if (threadIdx.x == 0) {
-      OutT v = r.value();
       if (direct) {
+        OutT v = r.value();
         if (inplace) v = reduce_op(out[row], v);
         out[row] = final_op(v);
       } else {
-        partial[row * n_seg + seg] = v;
+        partial[row * n_seg + seg] = r.carry();
       }
     }
     __syncthreads();  // s_warp is reused by the next row
+  }
+}
+
+// Folds the n_seg segment partials of every row (one warp per row, fixed order) and applies
+// init, inplace and final_op.
+template <typename OutT, typename ReduceOp, typename FinalOp, int TPB>
+__global__ void __launch_bounds__(TPB) row_finalize_kernel(OutT* __restrict__ out,
+                                                          const typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
+                                                          int64_t n_rows,
+                                                          int n_seg,
+                                                          OutT init,
+                                                          bool inplace,
+                                                          ReduceOp reduce_op,
+                                                          FinalOp final_op)
+{
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  const int lane       = threadIdx.x & 31;
+  const int64_t row    = int64_t(blockIdx.x) * (TPB / 32) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  State st;
+  init_state<OutT, State, isSum>(st, init, lane == 0);
+  for (int sgm = lane; sgm < n_seg; sgm += 32)
+    st.push_carry(partial[row * n_seg + sgm], reduce_op);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    State got = shfl_xor_any(st, off);
+    st.merge(got, reduce_op);
+  }
+  if (lane == 0) {
+    OutT v = st.value();
+    if (inplace) v = reduce_op(out[row], v);
+    out[row] = final_op(v);
   }
 }
 

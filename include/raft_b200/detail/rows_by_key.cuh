@@ -31,13 +31,14 @@
 #include "common.cuh"
 #include "launch.cuh"
 #include "ops.cuh"
+#include "rows_by_key_sorted.cuh"
 
 namespace raft_b200 {
 namespace detail {
 
 constexpr int kKeyTpb       = 512;  // 16 warps
 constexpr int kKeyMaxPerThr = 16;   // keys staged per thread per block -> B <= 8192
-constexpr int kKeyChunk     = 32;   // sorted entries per work item in private mode
+constexpr int kKeyChunk     = 16;   // sorted entries per work item in private mode
 
 struct RowsByKeyPlan {
   int vec;
@@ -406,6 +407,9 @@ template <typename DataT, typename SumT>
 inline size_t rows_by_key_scratch_bytes(const DataT* A, int64_t lda, int64_t nrows, int64_t ncols, int64_t nkeys)
 {
   if (nrows <= 0 || ncols <= 0 || nkeys <= 0) return 0;
+  if (tuning().key_algo != 1 && rows_by_key_sorted_supported(nrows, ncols, nkeys))
+    return plan_rows_by_key_sorted<DataT>(A, lda, nrows, ncols, nkeys,
+                                          sizeof(typename sum_state<SumT>::type::carry_t)).total;
   const RowsByKeyPlan p = plan_rows_by_key<DataT, SumT>(A, lda, nrows, ncols, nkeys);
   return p.kps == 0 ? 0 : p.scratch_sums + p.scratch_counts;
 }
@@ -436,6 +440,9 @@ cudaError_t launch_rows_by_key(SumT* sums,
     }
     return cudaSuccess;
   }
+  if (tuning().key_algo != 1 && rows_by_key_sorted_supported(nrows, ncols, nkeys))
+    return launch_rows_by_key_sorted<DataT, KeyT, WeightT, SumT>(sums, counts, A, lda, keys, weights, nrows, ncols,
+                                                                 nkeys, reset, stream, ws);
   constexpr int V16     = vec16<DataT>::value;
   const RowsByKeyPlan p = plan_rows_by_key<DataT, SumT>(A, lda, nrows, ncols, nkeys);
   if (p.kps == 0 || ncols > int64_t(0x7fffffff) || nkeys > int64_t(0x7fffffff)) {

@@ -179,10 +179,19 @@ static inline double load_elem(const void* p, int dtype, int64_t i)
   }
 }
 
-static inline double apply_main(double x, int main_op)
+/* main_op runs in the INPUT element type, as in the reference (raft::sq_op on a float returns
+ * a float, core/operators.hpp:93-100; a half is squared in float, :102-106). */
+static inline double apply_main(double x, int main_op, int in_dtype)
 {
   switch (main_op) {
-    case MAIN_SQ: return x * x;
+    case MAIN_SQ: {
+      if (in_dtype == DT_F32 || in_dtype == DT_F16) {
+        const volatile float f = (float)x;
+        const volatile float p = f * f;
+        return (double)p;
+      }
+      return x * x;
+    }
     case MAIN_ABS: return fabs(x);
     case MAIN_NZ: return x != 0.0 ? 1.0 : 0.0;
     default: return x;
@@ -232,7 +241,7 @@ EXPORT int oracle_reduce(const void* in, int in_dtype, int layout, int apply, in
           akey = j;
         }
       } else {
-        const double v = apply_main(x, main_op);
+        const double v = apply_main(x, main_op, in_dtype);
         if (reduce_op == RED_ADD) {
           const double t = acc + v;
           comp += fabs(acc) >= fabs(v) ? (acc - t) + v : (v - t) + acc;

@@ -60,7 +60,10 @@ size_t reduce_workspace(const b2r_reduce_desc& d, const InT* in)
 {
   const ReduceGeometry g = geometry(d);
   if (g.n_out <= 0) return 0;
-  if (g.contiguous) return detail::row_reduce_scratch_bytes<OutT>(g.n_out, g.n_red, sizeof(InT), nullptr);
+  if (g.contiguous) {
+    using CarryT = typename detail::state_for<OutT, ReduceOp>::type::carry_t;
+    return detail::row_reduce_scratch_bytes<CarryT>(g.n_out, g.n_red, sizeof(InT), nullptr);
+  }
   return detail::col_reduce_scratch_bytes<InT, OutT, ReduceOp>(in, g.n_red, g.n_out, g.n_out);
 }
 

@@ -67,6 +67,31 @@ def test_rows_by_key_skewed_and_missing_keys(cuda, oracle):
     assert np.array_equal(counts.cpu().numpy(), ecnt)
 
 
+@pytest.mark.parametrize("nobs,cols,nkeys", [(128, 32, 6), (100000, 37, 2048), (60000, 128, 1024), (512, 1024, 40)])
+def test_rows_by_key_table_algorithm(cuda, oracle, monkeypatch, nobs, cols, nkeys):
+    # the shared-memory-table kernel is the fallback for more keys than the sort kernel's
+    # histogram holds; B2R_KEY_ALGO=1 forces it for ordinary sizes
+    monkeypatch.setenv("B2R_KEY_ALGO", "1")
+    A, hA = device_synth((nobs, cols), np.float32, 31, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((nobs,), np.int32, 32, "int", 0, nkeys, cuda)
+    w, hw = device_synth((nobs,), np.float32, 33, "uniform", 0, 2, cuda)
+    counts = torch.empty(nkeys, dtype=torch.int64, device=cuda)
+    sums = linalg.reduce_rows_by_key(A, keys, nkeys, d_weights=w, counts=counts)
+    esum, ecnt = oracle.rows_by_key(hA, hk, nkeys, weights=hw)
+    oracle.assert_approx(esum, sums.cpu().numpy(), 1e-5)
+    assert np.array_equal(counts.cpu().numpy(), ecnt)
+
+
+def test_rows_by_key_many_keys(cuda, oracle):
+    # more keys than the sort kernel's shared-memory histogram holds -> table algorithm
+    nobs, cols, nkeys = 200000, 16, 60000
+    A, hA = device_synth((nobs, cols), np.float32, 41, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((nobs,), np.int32, 42, "int", 0, nkeys, cuda)
+    sums = linalg.reduce_rows_by_key(A, keys, nkeys)
+    esum, _ = oracle.rows_by_key(hA, hk, nkeys)
+    oracle.assert_approx(esum, sums.cpu().numpy(), 1e-5)
+
+
 def test_rows_by_key_empty(cuda):
     A = torch.empty((0, 16), dtype=torch.float32, device=cuda)
     keys = torch.empty((0,), dtype=torch.int32, device=cuda)

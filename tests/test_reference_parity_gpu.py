@@ -62,8 +62,12 @@ def test_strided_against_reference(cuda, oracle, ref, main, red, fin, scalar, ro
     assert st == 0
     ours = linalg.reduce(d, apply, main_op=main, reduce_op=red, final_op=fin, final_scalar=scalar)
     exp = oracle.reduce(host, apply=apply, layout=layout, main_op=main, reduce_op=red, final_op=fin, final_scalar=scalar)
-    oracle.assert_approx(exp, theirs.cpu().numpy(), 1e-5, "reference vs oracle")
-    oracle.assert_approx(theirs.cpu().numpy(), ours.cpu().numpy(), 1e-5, "ours vs reference")
+    # the reference's strided sum adds per-block results with fp32 atomics in scheduling order
+    # (linalg/detail/strided_reduction.cuh:54-76): with 200000 rows it is only good to ~5e-5
+    ref_tol = 1e-5 if rows <= 20000 else 2e-4
+    oracle.assert_approx(exp, theirs.cpu().numpy(), ref_tol, "reference vs oracle")
+    oracle.assert_approx(theirs.cpu().numpy(), ours.cpu().numpy(), ref_tol, "ours vs reference")
+    oracle.assert_approx(exp, ours.cpu().numpy(), 1e-5, "ours vs oracle")
 
 
 @pytest.mark.parametrize("op", ["argmin", "argmax"])
