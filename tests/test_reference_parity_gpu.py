@@ -98,9 +98,11 @@ def test_rows_by_key_against_reference(cuda, oracle, ref, nobs, cols, nkeys, wei
     assert ref.rows_by_key(theirs, A, keys, nkeys, weights=w) == 0
     ours = linalg.reduce_rows_by_key(A, keys, nkeys, d_weights=w)
     exp, _ = oracle.rows_by_key(hA, hk, nkeys, weights=hw)
-    # the reference adds in fp32 with atomics in scheduling order: looser than the product's own bound
-    oracle.assert_approx(exp, theirs.cpu().numpy(), 1e-4, "reference vs oracle")
-    oracle.assert_approx(theirs.cpu().numpy(), ours.cpu().numpy(), 1e-4, "ours vs reference")
+    # the reference adds in fp32 with one global atomic per element, in scheduling order
+    # (linalg/detail/reduce_rows_by_key.cuh:299): thousands of rows per key leave it good to a
+    # few 1e-4 only, and the figure changes from run to run
+    oracle.assert_approx(exp, theirs.cpu().numpy(), 1e-3, "reference vs oracle")
+    oracle.assert_approx(theirs.cpu().numpy(), ours.cpu().numpy(), 1e-3, "ours vs reference")
     oracle.assert_approx(exp, ours.cpu().numpy(), 1e-5, "ours vs oracle")
 
 
