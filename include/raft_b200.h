@@ -202,6 +202,41 @@ B2R_API int b2r_reduce_cols_by_key(void* out,
                                    b2r_stream_t stream);
 
 /*
+ * Column sums of a row-major fp32 matrix without any allocation:
+ *     out[j] = final_op(sum over i of in[i][j]),   in [n_rows x n_cols], out [n_cols]
+ * This entry point has no counterpart in the reference. It is b2r_reduce's column path
+ * (identity main_op, add, init 0, not in place) for callers that may not allocate device
+ * memory and have no workspace to pass - for example a plugin called with only its input,
+ * its output and a stream, or a service that forbids allocator calls once it is serving,
+ * because cudaMalloc / cudaFree take driver-wide locks. The scratch the kernels need lives in
+ * a 1 MiB array inside the library image (present on every GPU that loads the library, for
+ * the life of the process); the call uses no cudaMalloc, cudaFree, cudaMallocAsync or any
+ * other allocating routine.
+ *  - The call needs (row ranges) x n_cols x 8 bytes of that array, where the number of row
+ *    ranges is the CTAs of one resident wave divided by the column tiles (128 columns each).
+ *    With the default launch shape on a 148-SM B200 that is at most 0.6 MiB for any n_rows and
+ *    n_cols, so every shape is accepted; a need above 1 MiB (a wider launch shape through
+ *    B2R_COL_CPS, a GPU with more SMs) returns B2R_ERR_TOO_LARGE and launches nothing.
+ *    b2r_column_sum_f32_noalloc_max_scratch() returns the limit, b2r_reduce_workspace_bytes()
+ *    the need of a shape.
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    before any stream capture begins on that device.
+ *  - All calls on a device share the one array. Its contents are fully rewritten by each call
+ *    before they are read, so nothing has to be cleared, but two calls that can run at the same
+ *    time on one device (different streams, or different host threads) race on it: serialise
+ *    them.
+ */
+B2R_API int b2r_column_sum_f32_noalloc(float* out,
+                                       const float* in,
+                                       int64_t n_rows,
+                                       int64_t n_cols,
+                                       int32_t final_op,
+                                       double final_scalar,
+                                       b2r_stream_t stream);
+
+B2R_API size_t b2r_column_sum_f32_noalloc_max_scratch(void);
+
+/*
  * Applies a final_op to a vector in place: v[i] = final_op(v[i]). Used by the multi-GPU
  * host layer, which all-reduces raw per-GPU partials and applies final_op afterwards; in the
  * reference the same step is the trailing unaryOp of linalg/detail/strided_reduction.cuh:194-195.
