@@ -171,11 +171,11 @@ struct GenericState {
   using carry_t = Acc;
   Acc v;
   B2R_DI void init(const Acc& i) { v = i; }
-  B2R_DI void push(const Acc& x, const Op& op) { v = op(v, x); }
-  B2R_DI void merge(const GenericState& o, const Op& op) { v = op(v, o.v); }
+  B2R_DI void push(const Acc& x, Op op) { v = op(v, x); }
+  B2R_DI void merge(const GenericState& o, Op op) { v = op(v, o.v); }
   B2R_DI Acc value() const { return v; }
   B2R_DI carry_t carry() const { return v; }
-  B2R_DI void push_carry(const carry_t& x, const Op& op) { v = op(v, x); }
+  B2R_DI void push_carry(const carry_t& x, Op op) { v = op(v, x); }
 };
 
 template <typename Acc>
@@ -189,7 +189,7 @@ struct CompensatedState {
     c = Acc(0);
   }
   template <typename Op>
-  B2R_DI void push(const Acc& x, const Op&)
+  B2R_DI void push(const Acc& x, Op)
   {
     const Acc t   = s + x;
     const bool ge = abs_any(s) >= abs_any(x);
@@ -199,7 +199,7 @@ struct CompensatedState {
     s = t;
   }
   template <typename Op>
-  B2R_DI void merge(const CompensatedState& o, const Op& op)
+  B2R_DI void merge(const CompensatedState& o, Op op)
   {
     push(o.s, op);
     c += o.c;
@@ -207,7 +207,7 @@ struct CompensatedState {
   B2R_DI Acc value() const { return s + c; }
   B2R_DI carry_t carry() const { return s + c; }
   template <typename Op>
-  B2R_DI void push_carry(const carry_t& x, const Op& op)
+  B2R_DI void push_carry(const carry_t& x, Op op)
   {
     push(x, op);
   }
@@ -222,19 +222,19 @@ struct WideSumState {
   double s;
   B2R_DI void init(const float& i) { s = double(i); }
   template <typename Op>
-  B2R_DI void push(const float& x, const Op&)
+  B2R_DI void push(const float& x, Op)
   {
     s += double(x);
   }
   template <typename Op>
-  B2R_DI void merge(const WideSumState& o, const Op&)
+  B2R_DI void merge(const WideSumState& o, Op)
   {
     s += o.s;
   }
   B2R_DI float value() const { return float(s); }
   B2R_DI carry_t carry() const { return s; }
   template <typename Op>
-  B2R_DI void push_carry(const carry_t& x, const Op&)
+  B2R_DI void push_carry(const carry_t& x, Op)
   {
     s += x;
   }
@@ -275,7 +275,7 @@ struct state_for {
 // exchanges is U/2 + U/4 + ... instead of U per step.
 // ---------------------------------------------------------------------------------------
 template <int U, typename State, typename Op>
-B2R_DI void subwarp_transpose_reduce(State (&st)[U], int lane_in_group, int G, const Op& op)
+B2R_DI void subwarp_transpose_reduce(State (&st)[U], int lane_in_group, int G, Op op)
 {
   static_assert((U & (U - 1)) == 0 && U >= 1 && U <= 32, "U must be a power of two");
 #pragma unroll
@@ -323,7 +323,7 @@ B2R_DI SubwarpLayout subwarp_layout(int lane_in_group, int G)
 // Block-wide merge of one state per thread through shared memory, fixed order (warp 0
 // folds the per-warp results serially), so the result does not depend on scheduling.
 template <typename State, typename Op>
-B2R_DI State block_merge(State st, const Op& op, State* smem /* >= nwarps entries */)
+B2R_DI State block_merge(State st, Op op, State* smem /* >= nwarps entries */)
 {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;

@@ -122,6 +122,21 @@ inline bool aligned16(const T* p)
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+template <typename D, typename S>
+__global__ void convert_kernel(D* dst, const S* src, int64_t n)
+{
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = static_cast<D>(src[i]);
+}
+
+template <typename D, typename S>
+inline cudaError_t launch_convert(D* dst, const S* src, int64_t n, cudaStream_t stream)
+{
+  if (n <= 0) return cudaSuccess;
+  convert_kernel<D, S><<<unsigned(ceil_div<int64_t>(n, 256)), 256, 0, stream>>>(dst, src, n);
+  return cudaGetLastError();
+}
+
 // ---------------------------------------------------------------------------------------
 // Row-wise (contiguous axis) reduction.
 // ---------------------------------------------------------------------------------------

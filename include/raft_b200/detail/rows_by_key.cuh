@@ -99,7 +99,6 @@ __global__ void __launch_bounds__(kKeyTpb, 1)
                              RowsByKeySmem<SumT> lay)
 {
   using State      = CompensatedState<SumT>;
-  constexpr int NW = kKeyTpb / 32;
   constexpr int Q  = 8;  // row loads in flight per lane
   extern __shared__ __align__(16) unsigned char smem_raw[];
   State* table              = reinterpret_cast<State*>(smem_raw + lay.table);

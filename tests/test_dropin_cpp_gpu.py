@@ -1,0 +1,29 @@
+"""Runs the C++ test program of the drop-in raft::linalg headers (tests/cpp/test_dropin.cu): the
+stand-alone build, and - when it was built - the overlay build that puts this repository's
+raft/linalg headers in front of the reference's own raft/core headers."""
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(binary):
+    r = subprocess.run([binary], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert r.returncode == 0 and "ALL PASSED" in r.stdout, r.stdout[-4000:]
+    assert "FAIL" not in r.stdout
+
+
+def test_dropin_standalone(cuda):
+    binary = os.path.join(HERE, "cpp", "test_dropin")
+    assert os.path.exists(binary), "build it with `make -C tests/cpp` (done by __graft_entry__.build())"
+    _run(binary)
+
+
+def test_dropin_overlay(cuda):
+    binary = os.path.join(HERE, "cpp", "test_dropin_overlay")
+    if not os.path.exists(binary):
+        pytest.skip("overlay build needs the reference checkout at build time")
+    _run(binary)
