@@ -41,6 +41,33 @@ B2R_DI void init_state(State& st, const OutT& init, bool first_lane)
   }
 }
 
+// state <- reduce_op(state, main_op(x, idx)): the one place an element enters a state.
+template <typename OutT, typename IdxT, typename State, typename InT, typename I, typename MainOp, typename ReduceOp>
+B2R_DI void push_element(State& st, const InT& x, I idx, MainOp& main_op, ReduceOp& reduce_op)
+{
+  st.push(OutT(main_op(x, IdxT(idx))), reduce_op);
+}
+
+// argmin / argmax of tagged values: the same result as argmin_op(state, {idx, x}) - smaller
+// (larger) value wins, equal values keep the lower key - written as one predicate and two
+// selects so that no key/value pair is materialised per element.
+template <typename OutT, typename IdxT, typename K, typename V, typename I>
+B2R_DI void push_element(GenericState<KeyValue<K, V>, op::ArgMin>& st, const V& x, I idx, op::ToKeyValue<K>&, op::ArgMin&)
+{
+  const K k       = K(idx);
+  const bool take = (x < st.v.value) | ((x == st.v.value) & (k < st.v.key));
+  st.v.value      = take ? x : st.v.value;
+  st.v.key        = take ? k : st.v.key;
+}
+template <typename OutT, typename IdxT, typename K, typename V, typename I>
+B2R_DI void push_element(GenericState<KeyValue<K, V>, op::ArgMax>& st, const V& x, I idx, op::ToKeyValue<K>&, op::ArgMax&)
+{
+  const K k       = K(idx);
+  const bool take = (x > st.v.value) | ((x == st.v.value) & (k < st.v.key));
+  st.v.value      = take ? x : st.v.value;
+  st.v.key        = take ? k : st.v.key;
+}
+
 template <typename InT,
           typename OutT,
           typename IdxT,
@@ -67,11 +94,13 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
 
-  const int lane = threadIdx.x & 31;
-  const int lig  = lane & (G - 1);   // lane in group
-  const int grp  = lane / G;         // group in warp
-  const int gpw  = 32 / G;           // groups per warp
-  const int nvec = row_len / VEC;    // VEC divides row_len on the vector path; VEC==1 otherwise
+  const int lane  = threadIdx.x & 31;
+  const int lg    = 31 - __clz(G);    // G is a power of two
+  const int lig   = lane & (G - 1);   // lane in group
+  const int grp   = lane >> lg;       // group in warp
+  const int gsh   = 5 - lg;           // log2(groups per warp)
+  const int gpw   = 1 << gsh;         // groups per warp
+  const int nvec  = row_len / VEC;    // VEC divides row_len on the vector path; VEC==1 otherwise
 
   // A CTA owns a contiguous range of row batches (so that it streams one contiguous piece of
   // the matrix); its warps interleave inside the range.
@@ -81,14 +110,16 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
 
   if constexpr (MODE == kRows) {
     const int rows_per_batch = U * gpw;
-    int64_t n_batches        = (n_rows + rows_per_batch - 1) / rows_per_batch;
+    constexpr int ush        = ilog2_floor(U);
+    int64_t n_batches        = (n_rows + rows_per_batch - 1) >> (gsh + ush);
     n_batches                = n_batches < cta_first + batches_per_cta ? n_batches : cta_first + batches_per_cta;
     for (int64_t b = warp_global; b < n_batches; b += warps_total) {
       const int64_t row0 = b * rows_per_batch + grp;  // slot u -> row0 + u*gpw
       // slots of this group that are real rows; the others re-read the last real row (their
       // results are never stored), which keeps the load pattern uniform
       const int64_t left = n_rows - row0;
-      int valid          = left <= 0 ? 0 : int((left + gpw - 1) / gpw < U ? (left + gpw - 1) / gpw : U);
+      const int64_t slots = (left + gpw - 1) >> gsh;
+      const int valid     = left <= 0 ? 0 : int(slots < U ? slots : U);
       const InT* base    = data + (valid > 0 ? row0 : n_rows - 1) * ld;
       const int64_t step = valid > 0 ? int64_t(gpw) * ld : 0;
       State st[U];
@@ -105,7 +136,7 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
           for (int u = 0; u < U; ++u) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e)
-              st[u].push(OutT(main_op(v[u].e[e], IdxT(c * VEC + e))), reduce_op);
+              push_element<OutT, IdxT>(st[u], v[u].e[e], c * VEC + e, main_op, reduce_op);
           }
         }
       } else {
@@ -120,7 +151,7 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
           for (int u = 0; u < U; ++u) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e)
-              st[u].push(OutT(main_op(v[u].e[e], IdxT(c * VEC + e))), reduce_op);
+              push_element<OutT, IdxT>(st[u], v[u].e[e], c * VEC + e, main_op, reduce_op);
           }
         }
       }
@@ -143,7 +174,7 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
     }
   } else {
     // kChunks: one row per group, U chunks of it in flight per lane.
-    int64_t n_batches = (n_rows + gpw - 1) / gpw;
+    int64_t n_batches = (n_rows + gpw - 1) >> gsh;
     n_batches         = n_batches < cta_first + batches_per_cta ? n_batches : cta_first + batches_per_cta;
     for (int64_t b = warp_global; b < n_batches; b += warps_total) {
       const int64_t row = b * gpw + grp;
@@ -163,14 +194,14 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
         for (int u = 0; u < U; ++u) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e)
-            st[u].push(OutT(main_op(v[u].e[e], IdxT((c + u * G) * VEC + e))), reduce_op);
+            push_element<OutT, IdxT>(st[u], v[u].e[e], (c + u * G) * VEC + e, main_op, reduce_op);
         }
       }
       for (; c < nvec; c += G) {
         VecOf<InT, VEC> v = load_stream<InT, VEC>(rp + int64_t(c) * VEC);
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
-          st[0].push(OutT(main_op(v.e[e], IdxT(c * VEC + e))), reduce_op);
+          push_element<OutT, IdxT>(st[0], v.e[e], c * VEC + e, main_op, reduce_op);
       }
 #pragma unroll
       for (int u = 1; u < U; ++u)

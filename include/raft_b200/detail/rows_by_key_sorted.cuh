@@ -47,7 +47,10 @@ struct SortedPlan {
 //   offs [nkeys + 1]  first sorted position of each key          (exclusive prefix of counts)
 //   uoffs[nkeys + 1]  first unit of each key                     (exclusive prefix of unit counts)
 //   ukey/ubeg/ulen[max_units]  key, first sorted position and row count of each unit
-template <typename KeyT>
+// STAGED: the window's permutation is built in shared memory as 16-bit offsets (W <= 65536) and
+// written out with coalesced stores; otherwise every row's slot is stored straight to global
+// memory (32 sectors per warp store).
+template <typename KeyT, bool STAGED>
 __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restrict__ keys,
                                                            int64_t nrows,
                                                            int nkeys,
@@ -63,6 +66,7 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int* s_cnt   = reinterpret_cast<int*>(smem_raw);  // [nkeys] counts, then cursors
   int* s_cur   = s_cnt + nkeys;                     // [nkeys] scatter cursors
+  unsigned short* s_perm = reinterpret_cast<unsigned short*>(s_cur + nkeys);  // [W] when STAGED
   __shared__ int s_warp[2][kSortTpb / 32];
 
   const int win        = blockIdx.x;
@@ -163,9 +167,18 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
     for (int j = 0; j < KU; ++j) {
       if (kk[j] >= 0) {
         const int pos = atomicAdd(&s_cur[kk[j]], 1);
-        wperm[pos]    = static_cast<unsigned>(i0 + int64_t(j) * kSortTpb + tid);
+        if constexpr (STAGED) {
+          s_perm[pos] = static_cast<unsigned short>(i0 + int64_t(j) * kSortTpb + tid);
+        } else {
+          wperm[pos] = static_cast<unsigned>(i0 + int64_t(j) * kSortTpb + tid);
+        }
       }
     }
+  }
+  if constexpr (STAGED) {
+    __syncthreads();
+    for (int64_t i = tid; i < n; i += kSortTpb)
+      wperm[i] = s_perm[i];
   }
 }
 
@@ -272,7 +285,8 @@ __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
   using CarryT = typename State::carry_t;
   const op::Add add{};
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  State* s_acc     = reinterpret_cast<State*>(smem_raw);  // [8][chunk]
+  State* s_acc     = reinterpret_cast<State*>(smem_raw);            // [8][chunk]
+  int2* s_rng      = reinterpret_cast<int2*>(s_acc + 8 * 128);      // [n_windows] unit range of key k
   __shared__ long long s_n[8];
   const int k      = blockIdx.x;
   const int lane   = threadIdx.x & 31;
@@ -282,8 +296,11 @@ __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
   long long n_rows_k = 0;
   for (int w = warp * 32 + lane; w < n_windows; w += 256) {
     const int* wo = offs + size_t(w) * (nkeys + 1);
+    const int* wu = uoffs + size_t(w) * (nkeys + 1);
     n_rows_k += wo[k + 1] - wo[k];
+    s_rng[w] = make_int2(wu[k], wu[k + 1]);
   }
+  __syncthreads();
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1)
     n_rows_k += __shfl_xor_sync(0xffffffffu, n_rows_k, off);
@@ -294,16 +311,35 @@ __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
 #pragma unroll
     for (int e = 0; e < 4; ++e)
       acc[e].init(SumT(0));
-    for (int w = warp; w < n_windows; w += 8) {
-      const int* wu         = uoffs + size_t(w) * (nkeys + 1);
-      const int u0          = wu[k];
-      const int u1          = wu[k + 1];
-      const CarryT* wpart   = partial + size_t(w) * max_units * ncols;
-      for (int u = u0; u < u1; ++u) {
+    // four windows per step: the first unit row of each (most keys have one or two units per
+    // window) is loaded before any of them is consumed, so four loads per lane are in flight
+    for (int w0 = warp; w0 < n_windows; w0 += 32) {
+      int2 rng[4];
+      CarryT first[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int w = w0 + 8 * j;
+        rng[j]      = w < n_windows ? s_rng[w] : make_int2(0, 0);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = c0 + e * 32 + lane;
-          if (c < ncols) acc[e].push_carry(wpart[size_t(u) * ncols + c], add);
+          first[j][e] = (rng[j].y > rng[j].x && c < ncols)
+                          ? partial[(size_t(w) * max_units + rng[j].x) * ncols + c]
+                          : CarryT(0);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          acc[e].push_carry(first[j][e], add);
+        const CarryT* wpart = partial + size_t(w0 + 8 * j) * max_units * ncols;
+        for (int u = rng[j].x + 1; u < rng[j].y; ++u) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = c0 + e * 32 + lane;
+            if (c < ncols) acc[e].push_carry(wpart[size_t(u) * ncols + c], add);
+          }
         }
       }
     }
@@ -405,8 +441,11 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   CarryT* partial     = reinterpret_cast<CarryT*>(base + p.off_part);
   cudaError_t e;
 
-  const size_t sort_smem = size_t(nkeys) * 2 * sizeof(int);
-  auto sort_kern         = rbk_sort_kernel<KeyT>;
+  const size_t hist_smem   = size_t(nkeys) * 2 * sizeof(int);
+  const size_t staged_smem = hist_smem + size_t(p.window_rows) * sizeof(unsigned short);
+  const bool staged        = p.window_rows <= 65536 && staged_smem <= (size_t(220) << 10);
+  const size_t sort_smem   = staged ? staged_smem : hist_smem;
+  auto sort_kern           = staged ? rbk_sort_kernel<KeyT, true> : rbk_sort_kernel<KeyT, false>;
   if (sort_smem > (size_t(48) << 10)) {
     e = cudaFuncSetAttribute(sort_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sort_smem));
     if (e != cudaSuccess) return e;
@@ -440,7 +479,12 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
-  const size_t merge_smem = size_t(8) * 128 * sizeof(typename sum_state<SumT>::type);
+  const size_t merge_smem =
+    size_t(8) * 128 * sizeof(typename sum_state<SumT>::type) + size_t(p.n_windows) * sizeof(int2);
+  if (merge_smem > (size_t(48) << 10)) {
+    e = cudaFuncSetAttribute(rbk_merge_kernel<SumT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(merge_smem));
+    if (e != cudaSuccess) return e;
+  }
   rbk_merge_kernel<SumT><<<unsigned(nkeys), 256, merge_smem, stream>>>(
     sums, counts, partial, offs, uoffs, p.n_windows, p.max_units, int(ncols), int(nkeys), reset);
   return cudaGetLastError();
