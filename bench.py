@@ -79,14 +79,8 @@ class Workload:
         self.rows, self.cols = rows, cols
         self.data = torch.empty((rows, cols), dtype=torch.float32, device=device)
         base = first_row * cols
-        self.copies, self.turn = None, 0
         if name == "c1":
             linalg.synth_fill(self.data, 0, "uniform", -1, 1, first_index=base)
-            if rows * cols * 4 <= L2_BYTES:
-                # the input alone would stay in L2: rotate over enough identical copies that the set
-                # is larger than L2, so every step reads its matrix from HBM
-                n_copies = (2 * L2_BYTES) // (rows * cols * 4) + 1
-                self.copies = [self.data] + [self.data.clone() for _ in range(n_copies - 1)]
         elif name in ("c2", "c2sq"):
             linalg.synth_fill(self.data, 1, "normal", first_index=base)
         elif name in ("c3", "c3mean"):
@@ -123,9 +117,6 @@ class Workload:
         torch.cuda.synchronize(device)
 
     def run(self, data=None, keys=None):
-        if data is None and self.copies is not None:
-            data = self.copies[self.turn]
-            self.turn = (self.turn + 1) % len(self.copies)
         data = self.data if data is None else data
         la, L, n = self.linalg, self.L, self.name
         if self.impl == "ours":
@@ -414,7 +405,7 @@ def main():
     from raft_b200 import _lib
     _lib.load()  # fail loudly if the extension is missing
     w = Workload(name, device, args.impl, first_row=rank * rows)
-    flush = rows * cols * 4 <= L2_BYTES and w.copies is None
+    flush = rows * cols * 4 <= L2_BYTES
     alg = algorithmic_bytes(name)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -479,9 +470,7 @@ def main():
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, no collective",
                        "l2": "L2 flushed by a 378 MB write before every step" if flush
-                       else (f"rotating over {len(w.copies)} copies of the input "
-                             f"({len(w.copies) * rows * cols * 4 >> 20} MB > 126 MB L2)" if w.copies is not None
-                             else f"input {rows * cols * 4 >> 20} MB per GPU > 126 MB L2")},
+                       else f"input {rows * cols * 4 >> 20} MB per GPU > 126 MB L2"},
             "rows_per_s": rows_per_s, "roofline": roof, "e2e": e2e,
             "gpu_launches": args.steps * launches_per_step(name) if args.impl == "ours" else 0,
             "clocks": sampler.summary() if sampler else None, "wall_s": t_wall}
@@ -511,7 +500,7 @@ def main():
                     continue
                 try:
                     ww = Workload(cn, device, impl)
-                    ms = time_steps(ww, 20, 3, r * c * 4 <= L2_BYTES and ww.copies is None)
+                    ms = time_steps(ww, 20, 3, r * c * 4 <= L2_BYTES)
                     a_ms = sum(ms) / len(ms)
                     g = algorithmic_bytes(cn) / (a_ms * 1e-3) / 1e9
                     ent[impl] = {"gbs": g, "best_gbs": algorithmic_bytes(cn) / (min(ms) * 1e-3) / 1e9,

@@ -446,7 +446,7 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   const bool staged        = p.window_rows <= 65536 && staged_smem <= (size_t(220) << 10);
   const size_t sort_smem   = staged ? staged_smem : hist_smem;
   auto sort_kern           = staged ? rbk_sort_kernel<KeyT, true> : rbk_sort_kernel<KeyT, false>;
-  if (sort_smem > (size_t(48) << 10)) {
+  if (sort_smem + 1024 > (size_t(48) << 10)) {  // static shared memory counts against the 48 KB too
     e = cudaFuncSetAttribute(sort_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sort_smem));
     if (e != cudaSuccess) return e;
   }
@@ -481,7 +481,7 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
 
   const size_t merge_smem =
     size_t(8) * 128 * sizeof(typename sum_state<SumT>::type) + size_t(p.n_windows) * sizeof(int2);
-  if (merge_smem > (size_t(48) << 10)) {
+  if (merge_smem + 1024 > (size_t(48) << 10)) {
     e = cudaFuncSetAttribute(rbk_merge_kernel<SumT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(merge_smem));
     if (e != cudaSuccess) return e;
   }
