@@ -125,18 +125,23 @@ __global__ void __launch_bounds__(TPB) col_finalize_kernel(OutT* __restrict__ ou
                                                           OutT init,
                                                           bool inplace,
                                                           ReduceOp reduce_op,
-                                                          FinalOp final_op)
+                                                          FinalOp final_op,
+                                                          const int* __restrict__ cta_status = nullptr)
 {
-  using State          = typename state_for<OutT, ReduceOp>::type;
-  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
-  const int64_t col    = int64_t(blockIdx.x) * TPB + threadIdx.x;
+  using State       = typename state_for<OutT, ReduceOp>::type;
+  const int64_t col = int64_t(blockIdx.x) * TPB + threadIdx.x;
   if (col >= n_cols) return;
   State st;
   st.init(init);  // for a sum this is the single place init enters
-  (void)isSum;
-  for (int p = 0; p < n_parts; ++p)
+  bool gave_up = false;
+  for (int p = 0; p < n_parts; ++p) {
     st.push_carry(partial[int64_t(p) * n_cols + col], reduce_op);
+    if (cta_status != nullptr) gave_up |= cta_status[p] != 0;
+  }
   OutT v = st.value();
+  if constexpr (std::is_floating_point<OutT>::value) {
+    if (gave_up) v = OutT(NAN);  // a producer CTA abandoned a bounded wait: make it visible
+  }
   if (inplace) v = reduce_op(out[col], v);
   out[col] = final_op(v);
 }

@@ -10,7 +10,9 @@
 #pragma once
 
 #include "col_reduce.cuh"
+#include "col_reduce_tma.cuh"
 #include "row_reduce.cuh"
+#include "row_reduce_tma.cuh"
 
 #include <cstdlib>
 
@@ -69,13 +71,20 @@ inline int sm_count()
 // Launch-shape knobs. The defaults are the measured best on B200; the environment
 // variables exist so that a benchmark can sweep them without rebuilding.
 struct Tuning {
-  int row_ctas_per_sm      = 0;   // B2R_ROW_CPS   row-kernel CTAs per SM (0: as many as are resident)
-  int row_chunk_threshold  = 4;   // B2R_ROW_CHUNK rows with >= this many vectors per lane use kChunks
+  int row_ctas_per_sm      = 0;   // B2R_ROW_CPS   row-kernel CTAs per SM (0: twice the resident number)
+  int row_chunk_threshold  = 4;   // B2R_ROW_CHUNK rows with >= this many passes per lane use kChunks
+  int row_cpl              = 0;   // B2R_ROW_CPL   chunks of a row per lane and pass: 1, 2, 4 (0: by row length)
   int col_ctas_per_sm      = 4;   // B2R_COL_CPS   column-partial CTAs per SM (one resident wave)
   int split_ctas_per_sm    = 4;   // B2R_SPLIT_CPS
   int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
   int key_algo             = 0;     // B2R_KEY_ALGO   0: auto, 1: shared-memory table, 2: sort then stream
+  int col_tma              = 1;     // B2R_COL_TMA    1: TMA-staged tiles for narrow contiguous column reductions, 2: off
+  int col_tma_tile_kb      = 32;    // B2R_COL_TMA_KB tile size of the TMA ring, KiB
+  int tma_stages           = 4;     // B2R_TMA_STAGES stages of the TMA ring (2..8)
+  int row_tma              = 0;     // B2R_ROW_TMA    1: TMA-staged tiles for short contiguous rows
+  int row_tma_tile_kb      = 16;    // B2R_ROW_TMA_KB tile size of the row kernel's TMA ring, KiB
+  int row_tma_stages       = 3;     // B2R_ROW_TMA_STAGES
 };
 
 inline int env_int(const char* name, int dflt)
@@ -92,17 +101,28 @@ inline Tuning tuning()
   Tuning x;
   x.row_ctas_per_sm      = env_int("B2R_ROW_CPS", x.row_ctas_per_sm);
   x.row_chunk_threshold  = env_int("B2R_ROW_CHUNK", x.row_chunk_threshold);
+  x.row_cpl              = env_int("B2R_ROW_CPL", x.row_cpl);
   x.col_ctas_per_sm      = env_int("B2R_COL_CPS", x.col_ctas_per_sm);
   x.split_ctas_per_sm    = env_int("B2R_SPLIT_CPS", x.split_ctas_per_sm);
   x.key_block_rows       = env_int("B2R_KEY_BLOCK", x.key_block_rows);
   x.key_window_rows      = env_int("B2R_KEY_WINDOW", x.key_window_rows);
   x.key_algo             = env_int("B2R_KEY_ALGO", x.key_algo);
+  x.col_tma              = env_int("B2R_COL_TMA", x.col_tma);
+  x.col_tma_tile_kb      = env_int("B2R_COL_TMA_KB", x.col_tma_tile_kb);
+  x.tma_stages           = env_int("B2R_TMA_STAGES", x.tma_stages);
+  if (x.tma_stages < 2) x.tma_stages = 2;
+  if (x.tma_stages > 8) x.tma_stages = 8;
+  x.row_tma              = env_int("B2R_ROW_TMA", x.row_tma);
+  x.row_tma_tile_kb      = env_int("B2R_ROW_TMA_KB", x.row_tma_tile_kb);
+  x.row_tma_stages       = env_int("B2R_ROW_TMA_STAGES", x.row_tma_stages);
+  if (x.row_tma_stages < 2) x.row_tma_stages = 2;
+  if (x.row_tma_stages > 8) x.row_tma_stages = 8;
   return x;
 }
 
-// Resident CTAs per SM of a kernel: the reductions launch exactly one resident wave and loop
-// inside the kernel (measured on B200: one wave of long-lived CTAs reads ~15 % faster than
-// many short ones).
+// Resident CTAs per SM of a kernel: the reductions launch one or two resident waves of
+// long-lived CTAs and loop inside the kernel (measured on B200: ~15 % faster than many short
+// CTAs; two waves' worth of CTAs balance the tail a little better than exactly one).
 template <typename Kernel>
 inline int resident_ctas(Kernel kern, int tpb, size_t smem)
 {
@@ -218,21 +238,53 @@ cudaError_t launch_row_reduce(OutT* out,
 
   const int vec        = vec_ok ? V16 : 1;
   const int nvec       = int(row_len / vec);
-  unsigned g           = next_pow2(unsigned(nvec > 0 ? nvec : 1));
+  // lanes per row and chunks per lane: a lane sums up to four chunks of a row by itself (fewer
+  // exchanges afterwards), as long as a group still reads at least 64 contiguous bytes per load
+  int cpl              = tuning().row_cpl;
+  if (cpl == 0) cpl = nvec >= 32 ? 4 : (nvec >= 8 ? 2 : 1);
+  if (cpl != 1 && cpl != 2 && cpl != 4) cpl = 1;
+  unsigned g           = next_pow2(unsigned(nvec > 0 ? ceil_div<int>(nvec, cpl) : 1));
   const int G          = int(g > 32u ? 32u : g);
-  const bool chunks    = nvec >= G * tuning().row_chunk_threshold;
+  const bool chunks    = nvec >= G * cpl * tuning().row_chunk_threshold;
   const int gpw        = 32 / G;
-  const int64_t per_b  = chunks ? gpw : int64_t(U) * gpw;
+  // TMA-staged variant: short contiguous rows, plenty of them
+  if constexpr (V16 > 1) {
+    const size_t row_bytes = size_t(row_len) * sizeof(InT);
+    if (tuning().row_tma == 1 && vec_ok && !chunks && ld == row_len && n_rows >= 16384 && sizeof(OutT) <= 8) {
+      constexpr int UT   = 4;  // rows per group at a time: shared-memory latency needs less unrolling
+      const int64_t unit = int64_t(kTmaConsumers / 32) * UT * gpw;  // rows of one batch per consumer warp
+      int64_t k          = int64_t((size_t(tuning().row_tma_tile_kb) << 10) / (size_t(unit) * row_bytes));
+      if (k < 1) k = 1;
+      const int64_t tile_rows = unit * k;
+      const int stages        = tuning().row_tma_stages;
+      const size_t smem       = size_t(stages) * ((size_t(tile_rows) * row_bytes + 127) / 128 * 128);
+      if (smem <= (size_t(220) << 10)) {
+        auto kern      = row_reduce_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, UT>;
+        cudaError_t ea = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (ea != cudaSuccess) return ea;
+        int64_t ctas = int64_t(sm_count()) * resident_ctas(kern, kTmaThreads, smem);
+        int64_t rpc  = ceil_div<int64_t>(n_rows, ctas);
+        rpc          = ceil_div<int64_t>(rpc, tile_rows) * tile_rows;
+        ctas         = ceil_div<int64_t>(n_rows, rpc);
+        kern<<<unsigned(ctas), kTmaThreads, smem, stream>>>(out, data, n_rows, int(row_len), init, inplace, main_op,
+                                                           reduce_op, final_op, G, int(tile_rows), rpc, stages,
+                                                           nullptr);
+        return cudaGetLastError();
+      }
+    }
+  }
+  const int u_rows     = chunks ? 1 : U / cpl;  // rows per group and pass
+  const int64_t per_b  = int64_t(u_rows) * gpw;
   const int64_t n_b    = ceil_div<int64_t>(n_rows, per_b);
   const int rl         = int(row_len);
   const int cps_knob   = tuning().row_ctas_per_sm;
   const int sms        = sm_count();
 
-#define B2R_LAUNCH_ROW(VEC_, MODE_)                                                              \
+#define B2R_LAUNCH_ROW(VEC_, MODE_, U_, CPL_)                                                    \
   do {                                                                                           \
-    auto kern      = row_reduce_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, U, MODE_, TPB>; \
+    auto kern      = row_reduce_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, U_, MODE_, TPB, CPL_>; \
     static int occ = resident_ctas(kern, TPB, 0);                                                \
-    int64_t ctas   = int64_t(sms) * (cps_knob > 0 ? cps_knob : occ);                             \
+    int64_t ctas   = int64_t(sms) * (cps_knob > 0 ? cps_knob : 2 * occ);                         \
     const int64_t most = ceil_div<int64_t>(n_b, TPB / 32);                                       \
     if (ctas > most) ctas = most;                                                                \
     int64_t bpc = ceil_div<int64_t>(n_b, ctas);                                                  \
@@ -243,15 +295,23 @@ cudaError_t launch_row_reduce(OutT* out,
   } while (0)
   if (vec_ok) {
     if (chunks) {
-      B2R_LAUNCH_ROW(V16, kChunks);
+      B2R_LAUNCH_ROW(V16, kChunks, U, 1);
+    } else if (cpl == 4) {
+      B2R_LAUNCH_ROW(V16, kRows, U / 4, 4);
+    } else if (cpl == 2) {
+      B2R_LAUNCH_ROW(V16, kRows, U / 2, 2);
     } else {
-      B2R_LAUNCH_ROW(V16, kRows);
+      B2R_LAUNCH_ROW(V16, kRows, U, 1);
     }
   } else {
     if (chunks) {
-      B2R_LAUNCH_ROW(1, kChunks);
+      B2R_LAUNCH_ROW(1, kChunks, U, 1);
+    } else if (cpl == 4) {
+      B2R_LAUNCH_ROW(1, kRows, U / 4, 4);
+    } else if (cpl == 2) {
+      B2R_LAUNCH_ROW(1, kRows, U / 2, 2);
     } else {
-      B2R_LAUNCH_ROW(1, kRows);
+      B2R_LAUNCH_ROW(1, kRows, U, 1);
     }
   }
 #undef B2R_LAUNCH_ROW
@@ -262,6 +322,10 @@ cudaError_t launch_row_reduce(OutT* out,
 // Column-wise (strided axis) reduction of a row-major matrix.
 // ---------------------------------------------------------------------------------------
 struct ColPlan {
+  bool tma;          // TMA-staged kernel (narrow, contiguous rows)
+  int tile_rows;     // rows per TMA tile
+  int stages;        // stages of the TMA ring
+  size_t off_status; // byte offset of the per-CTA status words inside the scratch
   int vec;
   int TX;
   int TY;
@@ -300,6 +364,36 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
   p.rows_per_cta = rpc;
   p.smem         = size_t(TPB) * p.vec * sizeof(State);
   p.scratch      = gy > 1 ? align_up(size_t(gy) * size_t(n_cols) * sizeof(typename State::carry_t), 256) : 0;
+  p.tma          = false;
+  p.tile_rows    = 0;
+  p.off_status   = 0;
+  // TMA-staged variant: rows contiguous, the whole width in one CTA, enough rows to stream
+  const size_t row_bytes = size_t(n_cols) * sizeof(InT);
+  if (tuning().col_tma == 1 && vec_ok && ld == n_cols && ncv <= kTmaConsumers && row_bytes % 16 == 0 &&
+      n_rows >= 8192) {
+    unsigned txp = next_pow2(unsigned(ncv));
+    p.TX         = int(txp);
+    p.TY         = kTmaConsumers / p.TX;
+    size_t tile  = size_t(tuning().col_tma_tile_kb) << 10;
+    int64_t tr   = int64_t(tile / row_bytes) / p.TY * p.TY;
+    if (tr < p.TY) tr = p.TY;
+    p.tile_rows  = int(tr);
+    int64_t ctas = sm_count();
+    int64_t rpc2 = ceil_div<int64_t>(n_rows, ctas);
+    rpc2         = ceil_div<int64_t>(rpc2, tr) * tr;
+    ctas         = ceil_div<int64_t>(n_rows, rpc2);
+    p.grid_x     = unsigned(ctas);
+    p.grid_y     = 1;
+    p.rows_per_cta = rpc2;
+    const size_t stage = (size_t(tr) * row_bytes + 127) / 128 * 128;
+    p.stages     = tuning().tma_stages;
+    p.smem       = size_t(p.stages) * stage + size_t(kTmaConsumers) * p.vec * sizeof(State);
+    const size_t parts = align_up(size_t(ctas) * size_t(n_cols) * sizeof(typename State::carry_t), 256);
+    p.off_status = parts;
+    const size_t need = parts + align_up(size_t(ctas) * sizeof(int), 256);
+    p.scratch    = p.scratch > need ? p.scratch : need;
+    p.tma        = ctas > 1 && p.smem <= (size_t(220) << 10);
+  }
   return p;
 }
 
@@ -342,6 +436,23 @@ cudaError_t launch_col_reduce(OutT* out,
   if (scratch.error() != cudaSuccess) return scratch.error();
   using CarryT    = typename State::carry_t;
   CarryT* partial = static_cast<CarryT*>(scratch.get());
+  if (p.tma) {
+    if constexpr (V16 > 1) {
+      int* cta_status = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch.get()) + p.off_status);
+      auto kern       = col_partial_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16>;
+      cudaError_t ea  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(p.smem));
+      if (ea != cudaSuccess) return ea;
+      kern<<<p.grid_x, kTmaThreads, p.smem, stream>>>(out, partial, data, n_rows, int(n_cols), init, inplace, main_op,
+                                                     reduce_op, final_op, p.TX, p.tile_rows, p.rows_per_cta,
+                                                     p.stages, cta_status);
+      ea = cudaGetLastError();
+      if (ea != cudaSuccess) return ea;
+      const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB));
+      col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin, TPB, 0, stream>>>(
+        out, partial, int(p.grid_x), n_cols, init, inplace, reduce_op, final_op, cta_status);
+      return cudaGetLastError();
+    }
+  }
   const dim3 grid(p.grid_x, p.grid_y);
 
   if (p.vec > 1) {

@@ -77,7 +77,8 @@ template <typename InT,
           int VEC,
           int U,
           int MODE,
-          int TPB>
+          int TPB,
+          int CPL = 1>
 __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_kernel(OutT* __restrict__ out,
                                                         const InT* __restrict__ data,
                                                         int64_t n_rows,
@@ -126,32 +127,48 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
 #pragma unroll
       for (int u = 0; u < U; ++u)
         init_state<OutT, State, isSum>(st[u], init, lig == 0);
-      if (valid == U) {
-        for (int c = lig; c < nvec; c += G) {
-          VecOf<InT, VEC> v[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u)
-            v[u] = load_stream<InT, VEC>(base + u * step + int64_t(c) * VEC);
+      // CPL chunks of every row per lane and pass: U * CPL loads are in flight per lane, and the
+      // more of a row one lane sums by itself the fewer exchanges the reduction below needs
+      for (int c0 = lig; c0 < nvec; c0 += G * CPL) {
+        VecOf<InT, VEC> v[U][CPL];
+        if (valid == U && c0 + (CPL - 1) * G < nvec) {
 #pragma unroll
           for (int u = 0; u < U; ++u) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e)
-              push_element<OutT, IdxT>(st[u], v[u].e[e], c * VEC + e, main_op, reduce_op);
+            for (int k = 0; k < CPL; ++k)
+              v[u][k] = load_stream<InT, VEC>(base + u * step + int64_t(c0 + k * G) * VEC);
           }
-        }
-      } else {
-        for (int c = lig; c < nvec; c += G) {
-          VecOf<InT, VEC> v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e)
+                push_element<OutT, IdxT>(st[u], v[u][k].e[e], (c0 + k * G) * VEC + e, main_op, reduce_op);
+            }
+          }
+        } else {
+          // ragged batch (fewer than U real rows) or ragged row end (fewer than CPL chunks left)
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const int uu = u < valid ? u : (valid > 0 ? valid - 1 : 0);
-            v[u]         = load_stream<InT, VEC>(base + uu * step + int64_t(c) * VEC);
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) {
+              const int c  = c0 + k * G;
+              const int cc = c < nvec ? c : c0;  // re-read a valid chunk, ignored below
+              v[u][k]      = load_stream<InT, VEC>(base + uu * step + int64_t(cc) * VEC);
+            }
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e)
-              push_element<OutT, IdxT>(st[u], v[u].e[e], c * VEC + e, main_op, reduce_op);
+            for (int k = 0; k < CPL; ++k) {
+              if (c0 + k * G < nvec) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                  push_element<OutT, IdxT>(st[u], v[u][k].e[e], (c0 + k * G) * VEC + e, main_op, reduce_op);
+              }
+            }
           }
         }
       }

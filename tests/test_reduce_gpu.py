@@ -219,6 +219,51 @@ def test_error_compensation(cuda, oracle):
     oracle.assert_approx(np.full(cols, rows * v), got.cpu().numpy(), 1e-5)
 
 
+@pytest.mark.parametrize("rows,cols", [(100000, 64), (65537, 128), (300001, 4), (20000, 1024), (9000, 36), (70000, 256)])
+@pytest.mark.parametrize("main,red,fin", [("identity", "add", "identity"), ("sq", "add", "sqrt"), ("abs", "max", "identity")])
+def test_strided_tma_staged(cuda, oracle, monkeypatch, rows, cols, main, red, fin):
+    # the TMA-staged column kernel (narrow contiguous matrices), forced on; same results as the
+    # register-staged kernel and within tolerance of the oracle
+    t, host = device_synth((rows, cols), np.float32, 17, "uniform", -1, 1, cuda)
+    plain = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin)
+    monkeypatch.setenv("B2R_COL_TMA", "1")
+    staged = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin)
+    ws = torch.empty(linalg.reduce_workspace_bytes(t, linalg.ALONG_COLUMNS, reduce_op=red), dtype=torch.uint8, device=cuda)
+    staged_ws = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin, workspace=ws)
+    exp = oracle.reduce(host, apply=1, main_op=main, reduce_op=red, final_op=fin)
+    assert not torch.isnan(staged).any()
+    oracle.assert_approx(exp, staged.cpu().numpy(), 1e-5, "tma vs oracle")
+    oracle.assert_approx(plain.cpu().numpy(), staged.cpu().numpy(), 1e-6, "tma vs register-staged")
+    assert torch.equal(staged, staged_ws)
+    td, hd = device_synth((rows, min(cols, 512)), np.float64, 18, "uniform", -1, 1, cuda)
+    got = linalg.reduce(td, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin)
+    oracle.assert_approx(oracle.reduce(hd, apply=1, main_op=main, reduce_op=red, final_op=fin), got.cpu().numpy(), 1e-9)
+
+
+@pytest.mark.parametrize("rows,cols", [(100000, 128), (65537, 64), (300001, 4), (20001, 500), (16384, 36), (70000, 256),
+                                       (50000, 96)])
+def test_rows_tma_staged(cuda, oracle, monkeypatch, rows, cols):
+    # the TMA-staged row kernel (short contiguous rows), forced on: sums, norms and argmin
+    t, host = device_synth((rows, cols), np.float32, 19, "int", -4, 5, cuda)
+    monkeypatch.setenv("B2R_ROW_TMA", "1")
+    got = linalg.reduce(t, linalg.ALONG_ROWS)
+    assert np.array_equal(got.cpu().numpy().astype(np.float64), host.astype(np.float64).sum(1))
+    got = linalg.norm(t, "L2", linalg.ALONG_ROWS, fin_op="sqrt")
+    oracle.assert_approx(oracle.reduce(host, main_op="sq", final_op="sqrt"), got.cpu().numpy(), 1e-6)
+    kv = linalg.reduce(t, linalg.ALONG_ROWS, main_op="to_kvp", reduce_op="argmin", init=float("inf"))
+    ek, ev = oracle.reduce(host, main_op="to_kvp", reduce_op="argmin", init=np.inf)
+    assert np.array_equal(kv.keys.cpu().numpy().astype(np.int64), ek)
+    assert np.array_equal(kv.values.cpu().numpy().astype(np.float64), ev)
+    prev = got.clone()
+    linalg.reduce(t, linalg.ALONG_ROWS, got, inplace=True, main_op="abs", reduce_op="max")
+    assert np.array_equal(got.cpu().numpy(), np.maximum(prev.cpu().numpy(), np.abs(host).max(1)))
+    tu, hu = device_synth((rows, cols), np.float32, 20, "uniform", -1, 1, cuda)
+    got = linalg.reduce(tu, linalg.ALONG_ROWS)
+    monkeypatch.delenv("B2R_ROW_TMA")
+    oracle.assert_approx(oracle.reduce(hu), got.cpu().numpy(), 1e-5)
+    oracle.assert_approx(linalg.reduce(tu, linalg.ALONG_ROWS).cpu().numpy(), got.cpu().numpy(), 1e-6)
+
+
 @pytest.mark.parametrize("rows,cols", [(0, 5), (5, 0), (1, 1), (1, 300), (300, 1), (2, 2)])
 def test_degenerate_shapes(cuda, oracle, rows, cols):
     t = torch.full((rows, cols), 2.0, dtype=torch.float32, device=cuda)
