@@ -117,6 +117,9 @@ __global__ void __launch_bounds__(TPB, 4) col_partial_kernel(OutT* __restrict__ 
   }
 }
 
+// One warp per column: the lanes fold the row-range partials p = lane, lane + 32, ... (loads of
+// different lanes and steps are independent), then a butterfly merges the 32 lane states. The
+// order is fixed, so the result is reproducible.
 template <typename OutT, typename ReduceOp, typename FinalOp, int TPB>
 __global__ void __launch_bounds__(TPB) col_finalize_kernel(OutT* __restrict__ out,
                                                           const typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
@@ -128,22 +131,36 @@ __global__ void __launch_bounds__(TPB) col_finalize_kernel(OutT* __restrict__ ou
                                                           FinalOp final_op,
                                                           const int* __restrict__ cta_status = nullptr)
 {
-  using State       = typename state_for<OutT, ReduceOp>::type;
-  const int64_t col = int64_t(blockIdx.x) * TPB + threadIdx.x;
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  const int lane       = threadIdx.x & 31;
+  const int64_t col    = int64_t(blockIdx.x) * (TPB / 32) + (threadIdx.x >> 5);
   if (col >= n_cols) return;
   State st;
-  st.init(init);  // for a sum this is the single place init enters
-  bool gave_up = false;
-  for (int p = 0; p < n_parts; ++p) {
+  if constexpr (isSum) {
+    st.init(lane == 0 ? init : OutT(0));  // init enters a sum once
+  } else {
+    st.init(init);
+  }
+  int gave_up = 0;
+  for (int p = lane; p < n_parts; p += 32) {
     st.push_carry(partial[int64_t(p) * n_cols + col], reduce_op);
-    if (cta_status != nullptr) gave_up |= cta_status[p] != 0;
+    if (cta_status != nullptr) gave_up |= cta_status[p];
   }
-  OutT v = st.value();
-  if constexpr (std::is_floating_point<OutT>::value) {
-    if (gave_up) v = OutT(NAN);  // a producer CTA abandoned a bounded wait: make it visible
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    State got = shfl_xor_any(st, off);
+    st.merge(got, reduce_op);
+    gave_up |= __shfl_xor_sync(0xffffffffu, gave_up, off);
   }
-  if (inplace) v = reduce_op(out[col], v);
-  out[col] = final_op(v);
+  if (lane == 0) {
+    OutT v = st.value();
+    if constexpr (std::is_floating_point<OutT>::value) {
+      if (gave_up != 0) v = OutT(NAN);  // a producer CTA abandoned a bounded wait: make it visible
+    }
+    if (inplace) v = reduce_op(out[col], v);
+    out[col] = final_op(v);
+  }
 }
 
 }  // namespace detail

@@ -447,7 +447,7 @@ cudaError_t launch_col_reduce(OutT* out,
                                                      p.stages, cta_status);
       ea = cudaGetLastError();
       if (ea != cudaSuccess) return ea;
-      const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB));
+      const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));
       col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin, TPB, 0, stream>>>(
         out, partial, int(p.grid_x), n_cols, init, inplace, reduce_op, final_op, cta_status);
       return cudaGetLastError();
@@ -466,7 +466,7 @@ cudaError_t launch_col_reduce(OutT* out,
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || p.grid_y == 1) return e;
-  const unsigned fin_ctas = unsigned(ceil_div<int64_t>(n_cols, TPB));
+  const unsigned fin_ctas = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));
   col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin_ctas, TPB, 0, stream>>>(
     out, partial, int(p.grid_y), n_cols, init, inplace, reduce_op, final_op);
   return cudaGetLastError();

@@ -6,7 +6,7 @@
 // process no allocator traffic after start-up (cudaMalloc and cudaFree take driver locks and
 // can stall every stream of the device), a plugin that is handed two pointers and a stream and
 // nothing else, or a process whose memory pools are disabled. For them this entry point runs
-// the SAME two kernels (col_partial_kernel, col_finalize_kernel) on a scratch array that is
+// the SAME kernels as the column path of b2r_reduce on a scratch array that is
 // part of the library image: kNoAllocScratchBytes of device memory on every GPU that loads the
 // library, held until the process exits.
 //
