@@ -70,8 +70,9 @@ def launches_per_step(name):
 class Workload:
     """Device-resident inputs and outputs of one config, plus `run()` = one step."""
 
-    def __init__(self, name, device, impl, first_row=0):
+    def __init__(self, name, device, impl, first_row=0, world=1):
         import torch
+        self.world = world
         from raft_b200 import _lib as L
         from raft_b200 import linalg
         self.name, self.impl, self.torch, self.linalg, self.L = name, impl, torch, linalg, L
@@ -126,6 +127,13 @@ class Workload:
                 la.norm(data, "L2", la.ALONG_ROWS, self.out, fin_op="sqrt")
             elif n == "c2sq":
                 la.norm(data, "L2", la.ALONG_ROWS, self.out)
+            elif n in ("c3", "c3mean") and self.world > 1:
+                # row-sharded: raw partial per GPU, NCCL all-reduce of 64 floats, then final_op
+                import torch.distributed as dist
+                la.reduce(data, la.ALONG_COLUMNS, self.out, workspace=self.ws)
+                dist.all_reduce(self.out)
+                if n == "c3mean":
+                    la.apply_final(self.out, "div_const", float(self.rows * self.world))
             elif n == "c3":
                 la.reduce(data, la.ALONG_COLUMNS, self.out, workspace=self.ws)
             elif n == "c3mean":
@@ -136,6 +144,10 @@ class Workload:
             elif n == "c5":
                 la.reduce_rows_by_key(data, self.keys if keys is None else keys, NKEYS, d_sums=self.out,
                                       counts=self.counts, workspace=self.ws)
+                if self.world > 1:
+                    import torch.distributed as dist
+                    dist.all_reduce(self.out)     # 1024 x 128 fp32 partial tables
+                    dist.all_reduce(self.counts)  # 1024 int64 counts
         else:
             r = self.ref
             st = 0
@@ -404,7 +416,7 @@ def main():
 
     from raft_b200 import _lib
     _lib.load()  # fail loudly if the extension is missing
-    w = Workload(name, device, args.impl, first_row=rank * rows)
+    w = Workload(name, device, args.impl, first_row=rank * rows, world=world)
     flush = rows * cols * 4 <= L2_BYTES
     alg = algorithmic_bytes(name)
 
@@ -468,7 +480,8 @@ def main():
     line = {"metric": "hbm_gb_per_s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, no collective",
+            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4") or world == 1
+                                                        else "per-GPU partials + NCCL all-reduce inside the step"),
                        "l2": "L2 flushed by a 378 MB write before every step" if flush
                        else f"input {rows * cols * 4 >> 20} MB per GPU > 126 MB L2"},
             "rows_per_s": rows_per_s, "roofline": roof, "e2e": e2e,

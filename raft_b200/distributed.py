@@ -36,13 +36,13 @@ def combine_partials(partial, reduce_op="add", group=None):
 def reduce_columns(shard, total_rows, init=0.0, main_op="identity", reduce_op="add", final_op="identity",
                    final_scalar=1.0, group=None):
     """Column reduction of a row-sharded row-major matrix; every rank gets the full result.
-    fp32 sums travel as fp64 partials, so the cross-rank addition does not cost accuracy."""
-    wide = reduce_op == "add" and shard.dtype == torch.float32
-    part = linalg.reduce(shard, linalg.ALONG_COLUMNS, init=init, main_op=main_op, reduce_op=reduce_op,
-                         out_dtype=torch.float64 if wide else None)
+    `total_rows` is the row count of the whole matrix (what a mean divides by is the caller's
+    final_scalar; it is accepted here so call sites read like the single-GPU call)."""
+    del total_rows
+    part = linalg.reduce(shard, linalg.ALONG_COLUMNS, init=init, main_op=main_op, reduce_op=reduce_op)
     combine_partials(part, reduce_op, group)
     linalg.apply_final(part, final_op, final_scalar)
-    return part.to(shard.dtype) if wide else part
+    return part
 
 
 def reduce_rows(shard, **kw):
