@@ -361,7 +361,30 @@ def e2e_measure(w, steps):
     return ms, h2d, d2h
 
 
+_REAL_STDOUT = None
+
+
+def _claim_stdout():
+    """Everything any library prints to stdout from here on (NCCL prints its version line there)
+    goes to stderr; the one JSON line is written to the real stdout by emit()."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    if _REAL_STDOUT is not None:
+        os.write(_REAL_STDOUT, data)
+    else:
+        os.write(1, data)
+
+
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
@@ -397,7 +420,7 @@ def main():
                 "config": {"workload": desc, "note": "oracle/_ref not built: OpenMP host port of the path"},
                 "cpu_baseline": cb, "rows_per_s": cb["rows_per_s"],
                 "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        emit(line)
         return
 
     import torch
@@ -524,7 +547,7 @@ def main():
                     ent[impl] = {"error": str(ex)[:200]}
             table[cn] = ent
         line["configs"] = table
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
