@@ -202,6 +202,28 @@ B2R_API int b2r_reduce_cols_by_key(void* out,
                                    b2r_stream_t stream);
 
 /*
+ * raft::matrix::argmin / argmax - matrix/argmin.cuh:27-39, matrix/argmax.cuh:27-39, kernel
+ * matrix/detail/math.cuh:291-352: out[r] = column index of the smallest / largest element of row r
+ * of a row-major [n_rows x n_cols] matrix; on equal values the lowest index wins (cub::ArgMin /
+ * cub::ArgMax). in_dtype: B2R_F32 or B2R_F64; out_dtype: B2R_I32 or B2R_I64.
+ */
+B2R_API int b2r_matrix_argmin(void* out,
+                              int32_t out_dtype,
+                              const void* in,
+                              int32_t in_dtype,
+                              int64_t n_rows,
+                              int64_t n_cols,
+                              b2r_stream_t stream);
+
+B2R_API int b2r_matrix_argmax(void* out,
+                              int32_t out_dtype,
+                              const void* in,
+                              int32_t in_dtype,
+                              int64_t n_rows,
+                              int64_t n_cols,
+                              b2r_stream_t stream);
+
+/*
  * Column sums of a row-major fp32 matrix without any allocation:
  *     out[j] = final_op(sum over i of in[i][j]),   in [n_rows x n_cols], out [n_cols]
  * This entry point has no counterpart in the reference. It is b2r_reduce's column path

@@ -178,13 +178,15 @@ inline size_t row_reduce_scratch_bytes(int64_t n_rows, int64_t row_len, size_t i
   return n_seg > 1 ? align_up(size_t(n_rows) * n_seg * sizeof(CarryT), 256) : 0;
 }
 
+// `out` may point to a type other than the accumulator type OutT (what final_op returns).
 template <typename InT,
           typename OutT,
           typename IdxT,
           typename MainOp,
           typename ReduceOp,
-          typename FinalOp>
-cudaError_t launch_row_reduce(OutT* out,
+          typename FinalOp,
+          typename StoreT = OutT>
+cudaError_t launch_row_reduce(StoreT* out,
                               const InT* data,
                               int64_t n_rows,
                               int64_t row_len,
@@ -220,17 +222,17 @@ cudaError_t launch_row_reduce(OutT* out,
     if (n_seg < 1) n_seg = 1;
     const dim3 grid{unsigned(n_seg), unsigned(n_rows < 65535 ? n_rows : 65535), 1u};
     if (vec_ok) {
-      row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, 4, TPB>
+      row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, 4, TPB, StoreT>
         <<<grid, TPB, 0, stream>>>(
           out, partial, data, n_rows, row_len, ld, init, inplace, main_op, reduce_op, final_op, seg_vecs);
     } else {
-      row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, 1, 4, TPB>
+      row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, 1, 4, TPB, StoreT>
         <<<grid, TPB, 0, stream>>>(
           out, partial, data, n_rows, row_len, ld, init, inplace, main_op, reduce_op, final_op, seg_vecs);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || n_seg == 1) return e;
-    row_finalize_kernel<OutT, ReduceOp, FinalOp, TPB>
+    row_finalize_kernel<OutT, ReduceOp, FinalOp, TPB, StoreT>
       <<<unsigned(ceil_div<int64_t>(n_rows, TPB / 32)), TPB, 0, stream>>>(
         out, partial, n_rows, n_seg, init, inplace, reduce_op, final_op);
     return cudaGetLastError();
@@ -259,7 +261,7 @@ cudaError_t launch_row_reduce(OutT* out,
       const int stages        = tuning().row_tma_stages;
       const size_t smem       = size_t(stages) * ((size_t(tile_rows) * row_bytes + 127) / 128 * 128);
       if (smem <= (size_t(220) << 10)) {
-        auto kern      = row_reduce_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, UT>;
+        auto kern      = row_reduce_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, UT, StoreT>;
         cudaError_t ea = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (ea != cudaSuccess) return ea;
         int64_t ctas = int64_t(sm_count()) * resident_ctas(kern, kTmaThreads, smem);
@@ -282,7 +284,7 @@ cudaError_t launch_row_reduce(OutT* out,
 
 #define B2R_LAUNCH_ROW(VEC_, MODE_, U_, CPL_)                                                    \
   do {                                                                                           \
-    auto kern      = row_reduce_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, U_, MODE_, TPB, CPL_>; \
+    auto kern      = row_reduce_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, U_, MODE_, TPB, CPL_, StoreT>; \
     static int occ = resident_ctas(kern, TPB, 0);                                                \
     int64_t ctas   = int64_t(sms) * (cps_knob > 0 ? cps_knob : 2 * occ);                         \
     const int64_t most = ceil_div<int64_t>(n_b, TPB / 32);                                       \

@@ -135,6 +135,17 @@ struct ArgMax {
   }
 };
 
+// {key, value} -> key, converted to the index type the caller stores (raft::key_op,
+// core/operators.hpp:51-57): the final op of an index-only argmin / argmax.
+template <typename IndexT>
+struct KeyOf {
+  template <typename KV>
+  B2R_HDI IndexT operator()(const KV& p) const
+  {
+    return IndexT(p.key);
+  }
+};
+
 // Final op chosen at run time (it runs once per output, so a switch costs nothing).
 enum FinalKind : int { kFinIdentity = 0, kFinSqrt = 1, kFinMulConst = 2, kFinDivConst = 3, kFinAbs = 4 };
 

@@ -16,8 +16,10 @@
 //                      the S partials per row go to scratch memory and a second, tiny
 //                      row_reduce_kernel pass folds them and applies init / inplace / final.
 //
-// Sums are compensated (CompensatedState); every other operator runs through
-// GenericState. main_op receives the index along the reduced axis, as in the reference.
+// fp32 sums are carried in fp64 (WideSumState), fp64 sums are compensated; every other operator
+// runs through GenericState. main_op receives the index along the reduced axis, as in the
+// reference. The stored type may differ from the accumulator type (StoreT = what final_op
+// returns, e.g. only the key of a key/value pair); such a reduction cannot run in place.
 #pragma once
 
 #include "common.cuh"
@@ -78,8 +80,9 @@ template <typename InT,
           int U,
           int MODE,
           int TPB,
-          int CPL = 1>
-__global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_kernel(OutT* __restrict__ out,
+          int CPL   = 1,
+          typename StoreT = OutT>
+__global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_kernel(StoreT* __restrict__ out,
                                                         const InT* __restrict__ data,
                                                         int64_t n_rows,
                                                         int row_len,
@@ -182,7 +185,9 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
             const int64_t r = row0 + int64_t(slot) * gpw;
             if (r < n_rows) {
               OutT v = st[i].value();
-              if (inplace) v = reduce_op(out[r], v);
+              if constexpr (std::is_same<StoreT, OutT>::value) {
+                if (inplace) v = reduce_op(out[r], v);
+              }
               out[r] = final_op(v);
             }
           }
@@ -229,7 +234,9 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
       }
       if (lig == 0 && row < n_rows) {
         OutT v = st[0].value();
-        if (inplace) v = reduce_op(out[row], v);
+        if constexpr (std::is_same<StoreT, OutT>::value) {
+          if (inplace) v = reduce_op(out[row], v);
+        }
         out[row] = final_op(v);
       }
     }
@@ -246,8 +253,9 @@ template <typename InT,
           typename FinalOp,
           int VEC,
           int U,
-          int TPB>
-__global__ void __launch_bounds__(TPB) row_split_kernel(OutT* __restrict__ out,
+          int TPB,
+          typename StoreT = OutT>
+__global__ void __launch_bounds__(TPB) row_split_kernel(StoreT* __restrict__ out,
                                                        typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
                                                        const InT* __restrict__ data,
                                                        int64_t n_rows,
@@ -304,7 +312,9 @@ __global__ void __launch_bounds__(TPB) row_split_kernel(OutT* __restrict__ out,
     if (threadIdx.x == 0) {
       if (direct) {
         OutT v = r.value();
-        if (inplace) v = reduce_op(out[row], v);
+        if constexpr (std::is_same<StoreT, OutT>::value) {
+          if (inplace) v = reduce_op(out[row], v);
+        }
         out[row] = final_op(v);
       } else {
         partial[row * n_seg + seg] = r.carry();
@@ -316,8 +326,8 @@ __global__ void __launch_bounds__(TPB) row_split_kernel(OutT* __restrict__ out,
 
 // Folds the n_seg segment partials of every row (one warp per row, fixed order) and applies
 // init, inplace and final_op.
-template <typename OutT, typename ReduceOp, typename FinalOp, int TPB>
-__global__ void __launch_bounds__(TPB) row_finalize_kernel(OutT* __restrict__ out,
+template <typename OutT, typename ReduceOp, typename FinalOp, int TPB, typename StoreT = OutT>
+__global__ void __launch_bounds__(TPB) row_finalize_kernel(StoreT* __restrict__ out,
                                                           const typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
                                                           int64_t n_rows,
                                                           int n_seg,
@@ -342,7 +352,9 @@ __global__ void __launch_bounds__(TPB) row_finalize_kernel(OutT* __restrict__ ou
   }
   if (lane == 0) {
     OutT v = st.value();
-    if (inplace) v = reduce_op(out[row], v);
+    if constexpr (std::is_same<StoreT, OutT>::value) {
+      if (inplace) v = reduce_op(out[row], v);
+    }
     out[row] = final_op(v);
   }
 }

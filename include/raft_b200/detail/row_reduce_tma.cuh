@@ -24,8 +24,9 @@ template <typename InT,
           typename ReduceOp,
           typename FinalOp,
           int VEC,
-          int U>
-__global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(OutT* __restrict__ out,
+          int U,
+          typename StoreT = OutT>
+__global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* __restrict__ out,
                                                                        const InT* __restrict__ data,
                                                                        int64_t n_rows,
                                                                        int row_len,
@@ -150,7 +151,9 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(OutT* __
             if (lr < nr) {
               const int64_t r = tile_row0 + lr;
               OutT v          = st[i].value();
-              if (inplace) v = reduce_op(out[r], v);
+              if constexpr (std::is_same<StoreT, OutT>::value) {
+                if (inplace) v = reduce_op(out[r], v);
+              }
               out[r] = final_op(v);
             }
           }
@@ -162,9 +165,9 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(OutT* __
   }
   if (t < n_tiles) {
     // a bounded wait ran out: make it visible - the rows this warp did not finish become NaN
-    if constexpr (std::is_floating_point<OutT>::value) {
+    if constexpr (std::is_floating_point<StoreT>::value) {
       for (int64_t r = r_beg + int64_t(t) * tile_rows + tid; r < r_end; r += kTmaConsumers)
-        out[r] = OutT(NAN);
+        out[r] = StoreT(NAN);
     }
   }
 }

@@ -290,6 +290,36 @@ def reduce_cols_by_key(data, keys, out=None, nkeys=0, reset_sums=True):
     return out
 
 
+def _matrix_arg(fn_name, data, out, index_dtype):
+    _require_cuda(data, "in")
+    if data.dim() != 2 or not data.is_contiguous():
+        raise ValueError("in must be a row-major matrix")
+    n_rows, n_cols = data.shape
+    if out is None:
+        out = torch.empty(n_rows, dtype=index_dtype, device=data.device)
+    if out.numel() != n_rows:
+        raise ValueError("Size of output vector must equal number of rows in input matrix.")
+    if data.dtype not in (torch.float32, torch.float64) or out.dtype not in (torch.int32, torch.int64):
+        raise L.B2RError(L.ERR_UNSUPPORTED, fn_name)
+    with torch.cuda.device(data.device):
+        st = getattr(L.load(), fn_name)(out.data_ptr(), _DTYPES[out.dtype], data.data_ptr(), _DTYPES[data.dtype],
+                                        n_rows, n_cols, _stream_ptr(data.device))
+    L.check(st, fn_name)
+    return out
+
+
+def argmin(data, out=None, index_dtype=torch.int32):
+    """raft::matrix::argmin (matrix/argmin.cuh:27-39): index of the smallest element of every row
+    of a row-major matrix, lowest index on ties."""
+    return _matrix_arg("b2r_matrix_argmin", data, out, index_dtype)
+
+
+def argmax(data, out=None, index_dtype=torch.int32):
+    """raft::matrix::argmax (matrix/argmax.cuh:27-39): index of the largest element of every row,
+    lowest index on ties."""
+    return _matrix_arg("b2r_matrix_argmax", data, out, index_dtype)
+
+
 def apply_final(v, final_op, final_scalar=1.0):
     """v[i] = final_op(v[i]) in place (the deferred final step of a sharded reduction)."""
     _require_cuda(v, "v")

@@ -15,6 +15,8 @@
 #include <raft/linalg/reduce_cols_by_key.cuh>
 #include <raft/linalg/reduce_rows_by_key.cuh>
 #include <raft/linalg/strided_reduction.cuh>
+#include <raft/matrix/argmax.cuh>
+#include <raft/matrix/argmin.cuh>
 
 #include <cmath>
 #include <cstdio>
@@ -362,6 +364,43 @@ static void test_cols_by_key(int rows, int cols, int nkeys)
   CHECK(all_approx(e, out.host(), 1e-3), name);
 }
 
+static void test_matrix_arg()
+{
+  // cpp/tests/matrix/argmin.cu:71-75 and argmax.cu:71-72: the same 3x4 matrix -> {0,3,3} / {3,0,2}
+  raft::resources handle;
+  std::vector<float> h = {0.1f, 0.2f, 0.3f, 0.4f, 0.4f, 0.3f, 0.2f, 0.1f, 0.2f, 0.3f, 0.5f, 0.0f};
+  DevBuf<float> d(h);
+  DevBuf<int> o(3);
+  auto in = raft::make_device_matrix_view<const float, std::uint32_t, raft::row_major>(d.p, 3u, 4u);
+  raft::matrix::argmin(handle, in, raft::make_device_vector_view<int, std::uint32_t>(o.p, 3u));
+  CHECK((o.host() == std::vector<int>{0, 3, 3}), "matrix::argmin known answer {0,3,3}");
+  raft::matrix::argmax(handle, in, raft::make_device_vector_view<int, std::uint32_t>(o.p, 3u));
+  CHECK((o.host() == std::vector<int>{3, 0, 2}), "matrix::argmax known answer {3,0,2}");
+  std::vector<double> hd(h.begin(), h.end());
+  DevBuf<double> dd(hd);
+  DevBuf<short> os(3);  // an index type the C ABI does not name: header-only kernels
+  auto ind = raft::make_device_matrix_view<const double, std::uint32_t, raft::row_major>(dd.p, 3u, 4u);
+  raft::matrix::argmin(handle, ind, raft::make_device_vector_view<short, std::uint32_t>(os.p, 3u));
+  CHECK((os.host() == std::vector<short>{0, 3, 3}), "matrix::argmin double -> short index");
+  const int rows = 5000, cols = 200;
+  auto big = random_matrix(rows, cols, 77);
+  for (size_t i = 0; i < big.size(); i += 5)
+    big[i] = -0.25f;  // ties
+  DevBuf<float> db(big);
+  DevBuf<int> ob(rows);
+  raft::matrix::argmin(handle, raft::make_device_matrix_view<const float, int, raft::row_major>(db.p, rows, cols),
+                       raft::make_device_vector_view<int, int>(ob.p, rows));
+  auto got = ob.host();
+  bool ok  = true;
+  for (int r = 0; r < rows && ok; ++r) {
+    int bk = 0;
+    for (int c = 1; c < cols; ++c)
+      if (big[size_t(r) * cols + c] < big[size_t(r) * cols + bk]) bk = c;
+    ok = got[r] == bk;
+  }
+  CHECK(ok, "matrix::argmin 5000x200 with ties (lowest index)");
+}
+
 static void test_errors()
 {
   raft::resources handle;
@@ -422,6 +461,7 @@ int main()
   test_rows_by_key(100000, 37, 2048, true);
   test_cols_by_key(9, 9999, 42);
   test_cols_by_key(1024, 1234, 127);
+  test_matrix_arg();
   test_errors();
   cudaDeviceSynchronize();
   const cudaError_t e = cudaGetLastError();

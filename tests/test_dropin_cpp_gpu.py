@@ -27,3 +27,12 @@ def test_dropin_overlay(cuda):
     if not os.path.exists(binary):
         pytest.skip("overlay build needs the reference checkout at build time")
     _run(binary)
+
+
+def test_reference_stats_on_overlay(cuda):
+    """The reference's own raft::stats::{sum, mean, stddev, vars, weighted_mean} headers compiled
+    on top of this repository's raft/linalg headers (tests/cpp/test_stats_overlay.cu)."""
+    binary = os.path.join(HERE, "cpp", "test_stats_overlay")
+    if not os.path.exists(binary):
+        pytest.skip("overlay build needs the reference checkout at build time")
+    _run(binary)
