@@ -14,9 +14,9 @@
  *  - every call is asynchronous on `stream` and never synchronises;
  *  - the return value is a b2r_status; B2R_ERR_CUDA means a CUDA runtime call failed and
  *    b2r_last_cuda_error() returns its cudaError_t (per host thread);
- *  - `workspace` may be NULL: kernels that need scratch memory then take it from the
- *    stream-ordered allocator (cudaMallocAsync on `stream`). A caller that wants no
- *    allocation inside the call passes b2r_*_workspace_bytes() bytes of device memory.
+ *  - `workspace` may be NULL: kernels that need scratch memory then take it from a
+ *    library-owned stream-ordered pool (allocation and free ordered on `stream`). A caller that
+ *    wants no allocation inside the call passes b2r_*_workspace_bytes() bytes of device memory.
  */
 #ifndef RAFT_B200_H
 #define RAFT_B200_H
@@ -288,6 +288,14 @@ B2R_API int b2r_synth_fill(void* dst,
                            double lo,
                            double hi,
                            b2r_stream_t stream);
+
+/*
+ * Scratch the library allocates for itself (calls made with workspace == NULL) comes from a
+ * stream-ordered memory pool the library owns, one per device, which keeps freed blocks for
+ * re-use. This call gives the cached blocks of the current device back to the driver. No
+ * counterpart in the reference (rmm plays this role there).
+ */
+B2R_API int b2r_trim_scratch_pool(void);
 
 B2R_API const char* b2r_status_string(int status);
 B2R_API int b2r_last_cuda_error(void);

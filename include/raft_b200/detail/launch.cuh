@@ -4,9 +4,9 @@
 //
 // All launchers are asynchronous on the given stream and return a cudaError_t; none of
 // them synchronises. Kernels that need scratch memory (row partials, column partials) take
-// it from the caller's workspace when one is passed and large enough, otherwise from the
-// stream-ordered allocator (cudaMallocAsync / cudaFreeAsync on the same stream), which is
-// what the reference does for its only scratch user (coalesced_reduction-inl.cuh:560).
+// it from the caller's workspace when one is passed and large enough, otherwise from a
+// library-owned stream-ordered pool (allocation and free ordered on the same stream), as the
+// reference does through rmm for its only scratch user (coalesced_reduction-inl.cuh:560).
 #pragma once
 
 #include "col_reduce.cuh"
@@ -24,6 +24,38 @@ struct Workspace {
   size_t bytes = 0;
 };
 
+// Library-owned stream-ordered memory pool, one per device, created on first use. The device's
+// default pool gives freed memory back to the driver at the next synchronisation, so a caller
+// that synchronises between calls would pay a fresh physical allocation (milliseconds) on every
+// call; this pool keeps what it has (release threshold = unlimited). b2r_trim_scratch_pool()
+// returns the cached memory. Falls back to the default pool if a pool cannot be created.
+inline cudaMemPool_t scratch_pool()
+{
+  static cudaMemPool_t pools[64] = {};
+  static bool tried[64]          = {};
+  int dev                        = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!tried[dev]) {
+    tried[dev]            = true;
+    cudaMemPoolProps prop = {};
+    prop.allocType        = cudaMemAllocationTypePinned;
+    prop.handleTypes      = cudaMemHandleTypeNone;
+    prop.location.type    = cudaMemLocationTypeDevice;
+    prop.location.id      = dev;
+    cudaMemPool_t pool    = nullptr;
+    if (cudaMemPoolCreate(&pool, &prop) == cudaSuccess) {
+      unsigned long long keep = ~0ull;
+      if (cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) == cudaSuccess) {
+        pools[dev] = pool;
+      } else {
+        cudaMemPoolDestroy(pool);
+      }
+    }
+    (void)cudaGetLastError();
+  }
+  return pools[dev];
+}
+
 // Stream-ordered scratch with a caller-provided fast path.
 class Scratch {
  public:
@@ -33,7 +65,8 @@ class Scratch {
     if (ws.ptr != nullptr && ws.bytes >= need) {
       ptr_ = ws.ptr;
     } else {
-      err_   = cudaMallocAsync(&ptr_, need, stream);
+      cudaMemPool_t pool = scratch_pool();
+      err_   = pool != nullptr ? cudaMallocFromPoolAsync(&ptr_, need, pool, stream) : cudaMallocAsync(&ptr_, need, stream);
       owned_ = err_ == cudaSuccess;
     }
   }
@@ -163,14 +196,15 @@ inline cudaError_t launch_convert(D* dst, const S* src, int64_t n, cudaStream_t 
 template <typename CarryT>
 inline size_t row_reduce_scratch_bytes(int64_t n_rows, int64_t row_len, size_t in_size, int* n_seg_out)
 {
-  // Split rows only when there are too few rows to occupy the machine with one warp per
-  // row and the rows are long enough that a segment still amortises a CTA.
+  // One warp per row leaves the machine idle when there are few rows: below 16 warps' worth of
+  // rows per SM, rows of 8 KB and more get a CTA each (n_seg = 1, no scratch), and are cut into
+  // segments of at least 32 KB when even that gives too few CTAs.
   const int sms           = sm_count();
   const int64_t row_bytes = row_len * int64_t(in_size);
-  int n_seg               = 1;
-  if (n_rows < int64_t(sms) * 8 && row_bytes >= (int64_t(64) << 10)) {
+  int n_seg               = 0;  // 0: warp-per-row kernels
+  if (n_rows < int64_t(sms) * 16 && row_bytes >= (int64_t(8) << 10)) {
     const int64_t want    = ceil_div<int64_t>(int64_t(sms) * tuning().split_ctas_per_sm, n_rows);
-    const int64_t max_seg = ceil_div<int64_t>(row_bytes, int64_t(32) << 10);
+    const int64_t max_seg = row_bytes / (int64_t(32) << 10);
     n_seg                 = int(want < max_seg ? want : max_seg);
     if (n_seg < 1) n_seg = 1;
   }
@@ -209,7 +243,8 @@ cudaError_t launch_row_reduce(StoreT* out,
   using CarryT      = typename state_for<OutT, ReduceOp>::type::carry_t;
   const size_t need = row_reduce_scratch_bytes<CarryT>(n_rows, row_len, sizeof(InT), &n_seg);
 
-  if (n_seg > 1 || row_len > int64_t(0x7fffffff)) {
+  if (n_seg >= 1 || row_len > int64_t(0x7fffffff)) {
+    if (n_seg < 1) n_seg = 1;
     // long rows: CTA per (segment, row), then fold the segment partials
     Scratch scratch(ws, need, stream);
     if (scratch.error() != cudaSuccess) return scratch.error();

@@ -254,6 +254,13 @@ int b2r_synth_fill(void* dst, int32_t dtype, int64_t n, int64_t first_index, uin
   return set_cuda_error(e);
 }
 
+int b2r_trim_scratch_pool(void)
+{
+  cudaMemPool_t pool = detail::scratch_pool();
+  if (pool == nullptr) return B2R_OK;
+  return set_cuda_error(cudaMemPoolTrimTo(pool, 0));
+}
+
 const char* b2r_status_string(int status)
 {
   switch (status) {
