@@ -64,7 +64,7 @@ def algorithmic_bytes(name):
 
 
 def launches_per_step(name):
-    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 3}[name]
+    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 6}[name]
 
 
 class Workload:

@@ -1,27 +1,35 @@
 // Keyed row sums, "sort then stream" formulation:
 //     sums[keys[i]][:] += w[i] * A[i][:]
 //
-// Three kernels, no floating-point atomics, every matrix row read from HBM exactly once:
+// Six kernels, no floating-point atomics, every matrix row read from HBM once:
 //
-//  rbk_sort_kernel     one CTA per window of W consecutive rows. Counting sort of the window's
-//                      row indices by key in shared memory (integer atomics only): writes
-//                        perm[window][.]        row offsets inside the window, grouped by key
-//                        unit tables            the grouped list cut into work units of at most
-//                                               kUnitRows rows that all carry one key
-//  rbk_stream_kernel   one warp per work unit, persistent grid: the warp streams the unit's
-//                      rows (a sub-warp of G lanes per row, 8 row loads in flight per lane),
-//                      keeps a compensated sum per column in REGISTERS, and writes one partial
-//                      row per unit. Nothing is shared between warps, so occupancy - and with
-//                      it the bytes in flight - is not limited by an accumulator table, long
-//                      runs of one key are spread over many warps (skew-proof), and a handful
-//                      of keys is as fast as thousands.
-//  rbk_merge_kernel    per (key, column): folds the partial rows of the key's units over all
-//                      windows in a fixed order (compensated), adds to or overwrites sums, and
-//                      derives the exact int64 row counts from the sort's offsets.
+//  rbk_sort_kernel     one CTA per window of W consecutive rows (W <= 65536, sized so that the
+//                      windows fill whole waves of resident CTAs). Counting sort of the window's row
+//                      offsets by key with integer shared-memory atomics: perm[window][.] (16-bit
+//                      offsets staged in shared memory, written out coalesced) and offs[window][k].
+//  rbk_count_kernel    rows of every key in every GROUP of consecutive windows. The group size is
+//                      chosen so that a key has about kUnitTarget rows per group, whatever the
+//                      number of keys (1 window for up to ~400 keys, 32 for 8192 and more).
+//  rbk_units_kernel    one CTA per group: prefix sum over the keys -> the work units (at most
+//                      kUnitCap rows of one key each, split evenly) and the list of (group, key)
+//                      pairs that got more than one unit.
+//  rbk_stream_kernel   one warp per work unit, units handed out dynamically: the warp finds the
+//                      unit's rows through the sorted windows (a search over at most 32 segment
+//                      counts held one per lane), streams them (a sub-warp of G lanes per row, 8 row
+//                      loads in flight per lane), keeps a wide / compensated sum per column in
+//                      REGISTERS and writes ONE partial row per unit. Nothing is shared between
+//                      warps, so occupancy - and with it the bytes in flight - is not limited by an
+//                      accumulator table; long runs of one key are spread over many warps
+//                      (skew-proof); a handful of keys is as fast as tens of thousands.
+//  rbk_fold_kernel     one warp per listed (group, key): folds its units' partial rows into the
+//                      first of them.
+//  rbk_merge_kernel    one warp (many keys) or one CTA (few keys) per key: folds the key's partial
+//                      rows over all groups in a fixed order, adds to or overwrites sums, and derives
+//                      the exact int64 row counts from the sort's offsets.
 //
-// Extra memory traffic over the matrix itself: the keys are read twice, the 4-byte permutation
-// is written and read once, and one partial row per unit is written and read - about 3 % for
-// 128 fp32 columns.
+// Extra memory traffic over the matrix itself: the keys are read twice, one 4-byte index per row
+// is written and read once, and one fp64 partial row per ~128 matrix rows is written and read -
+// about 4 % for 128 fp32 columns.
 #pragma once
 
 #include "common.cuh"
@@ -31,22 +39,24 @@
 namespace raft_b200 {
 namespace detail {
 
-constexpr int kUnitRows   = 256;    // rows per work unit (one key each)
-constexpr int kSortTpb    = 1024;
-constexpr int kMaxSortKeys = 49152;  // histogram + cursors must fit shared memory
+constexpr int kUnitTarget  = 128;    // rows per work unit aimed for
+constexpr int kUnitCap     = 192;    // rows per work unit at most
+constexpr int kMaxGroup    = 32;     // windows per group at most (one lane per window)
+constexpr int kSortTpb     = 1024;
+constexpr int kMaxSortKeys = 24576;  // histogram + cursors (8 bytes per key) must fit shared memory
 
 struct SortedPlan {
   int vec;
-  int window_rows;   // W
+  int window_rows;  // W, a multiple of 1024, at most 65536
   int n_windows;
-  int max_units;     // per window
-  size_t off_perm, off_offs, off_uoffs, off_ukey, off_ubeg, off_ulen, off_part, total;
+  int group;        // windows per group
+  int n_groups;
+  int max_units;    // per group
+  int max_fold;     // (group, key) pairs with more than one unit, at most
+  size_t off_perm, off_offs, off_gcnt, off_uoffs, off_ukey, off_ufirst, off_ulen, off_fold, off_counter, off_part,
+    total;
 };
 
-// Work-unit tables of one window (global memory):
-//   offs [nkeys + 1]  first sorted position of each key          (exclusive prefix of counts)
-//   uoffs[nkeys + 1]  first unit of each key                     (exclusive prefix of unit counts)
-//   ukey/ubeg/ulen[max_units]  key, first sorted position and row count of each unit
 // STAGED: the window's permutation is built in shared memory as 16-bit offsets (W <= 65536) and
 // written out with coalesced stores; otherwise every row's slot is stored straight to global
 // memory (32 sectors per warp store).
@@ -55,34 +65,30 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
                                                            int64_t nrows,
                                                            int nkeys,
                                                            int W,
-                                                           int max_units,
                                                            unsigned* __restrict__ perm,
                                                            int* __restrict__ offs,
-                                                           int* __restrict__ uoffs,
-                                                           int* __restrict__ ukey,
-                                                           int* __restrict__ ubeg,
-                                                           int* __restrict__ ulen)
+                                                           int* __restrict__ unit_counter)
 {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unit_counter[0] = 0;  // the stream kernel's work queue
+    unit_counter[1] = 0;  // length of the fold list
+  }
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  int* s_cnt   = reinterpret_cast<int*>(smem_raw);  // [nkeys] counts, then cursors
-  int* s_cur   = s_cnt + nkeys;                     // [nkeys] scatter cursors
+  int* s_cnt             = reinterpret_cast<int*>(smem_raw);                  // [nkeys] counts
+  int* s_cur             = s_cnt + nkeys;                                     // [nkeys] scatter cursors
   unsigned short* s_perm = reinterpret_cast<unsigned short*>(s_cur + nkeys);  // [W] when STAGED
-  __shared__ int s_warp[2][kSortTpb / 32];
+  __shared__ int s_warp[kSortTpb / 32];
 
-  const int win        = blockIdx.x;
-  const int64_t row0   = int64_t(win) * W;
-  int64_t n            = nrows - row0;
-  n                    = n < W ? n : W;
-  const int tid        = threadIdx.x;
-  const int lane       = tid & 31;
-  const int warp       = tid >> 5;
-  const KeyT* wkeys    = keys + row0;
-  unsigned* wperm      = perm + row0;
-  int* w_offs          = offs + size_t(win) * (nkeys + 1);
-  int* w_uoffs         = uoffs + size_t(win) * (nkeys + 1);
-  int* w_ukey          = ukey + size_t(win) * max_units;
-  int* w_ubeg          = ubeg + size_t(win) * max_units;
-  int* w_ulen          = ulen + size_t(win) * max_units;
+  const int win      = blockIdx.x;
+  const int64_t row0 = int64_t(win) * W;
+  int64_t n          = nrows - row0;
+  n                  = n < W ? n : W;
+  const int tid      = threadIdx.x;
+  const int lane     = tid & 31;
+  const int warp     = tid >> 5;
+  const KeyT* wkeys  = keys + row0;
+  unsigned* wperm    = perm + row0;
+  int* w_offs        = offs + size_t(win) * (nkeys + 1);
 
   for (int k = tid; k < nkeys; k += kSortTpb)
     s_cnt[k] = 0;
@@ -94,6 +100,7 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
     for (int j = 0; j < KU; ++j) {
       const int64_t i = i0 + int64_t(j) * kSortTpb + tid;
       kk[j]           = i < n ? static_cast<int>(wkeys[i]) : -1;
+      if (unsigned(kk[j]) >= unsigned(nkeys)) kk[j] = -1;  // a key outside [0, nkeys) drops its row
     }
 #pragma unroll
     for (int j = 0; j < KU; ++j)
@@ -101,60 +108,33 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
   }
   __syncthreads();
 
-  // exclusive scans of the counts and of the per-key unit counts, both over [0, nkeys)
+  // exclusive scan of the counts over [0, nkeys)
   const int per = (nkeys + kSortTpb - 1) / kSortTpb;
   const int b0  = tid * per;
-  int loc_c = 0, loc_u = 0;
-  for (int i = 0; i < per; ++i) {
-    if (b0 + i < nkeys) {
-      const int c = s_cnt[b0 + i];
-      loc_c += c;
-      loc_u += (c + kUnitRows - 1) / kUnitRows;
-    }
-  }
-  int inc_c = loc_c, inc_u = loc_u;
+  int local     = 0;
+  for (int i = 0; i < per; ++i)
+    if (b0 + i < nkeys) local += s_cnt[b0 + i];
+  int incl = local;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    const int a = __shfl_up_sync(0xffffffffu, inc_c, off);
-    const int b = __shfl_up_sync(0xffffffffu, inc_u, off);
-    if (lane >= off) {
-      inc_c += a;
-      inc_u += b;
-    }
+    const int a = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += a;
   }
-  if (lane == 31) {
-    s_warp[0][warp] = inc_c;
-    s_warp[1][warp] = inc_u;
-  }
+  if (lane == 31) s_warp[warp] = incl;
   __syncthreads();
-  int base_c = 0, base_u = 0;
-  for (int w = 0; w < warp; ++w) {
-    base_c += s_warp[0][w];
-    base_u += s_warp[1][w];
-  }
-  int run_c = base_c + inc_c - loc_c;
-  int run_u = base_u + inc_u - loc_u;
+  int base = 0;
+  for (int w = 0; w < warp; ++w)
+    base += s_warp[w];
+  int run = base + incl - local;
   for (int i = 0; i < per; ++i) {
     const int k = b0 + i;
     if (k < nkeys) {
-      const int c  = s_cnt[k];
-      const int nu = (c + kUnitRows - 1) / kUnitRows;
-      w_offs[k]    = run_c;
-      w_uoffs[k]   = run_u;
-      for (int u = 0; u < nu; ++u) {
-        w_ukey[run_u + u] = k;
-        w_ubeg[run_u + u] = run_c + u * kUnitRows;
-        w_ulen[run_u + u] = (c - u * kUnitRows) < kUnitRows ? (c - u * kUnitRows) : kUnitRows;
-      }
-      s_cur[k]     = run_c;
-      run_c += c;
-      run_u += nu;
+      w_offs[k] = run;
+      s_cur[k]  = run;
+      run += s_cnt[k];
     }
   }
-  if (tid == kSortTpb - 1) {
-    w_offs[nkeys]  = run_c;
-    w_uoffs[nkeys] = run_u;
-  }
+  if (tid == kSortTpb - 1) w_offs[nkeys] = run;
   __syncthreads();
   for (int64_t i0 = 0; i0 < n; i0 += int64_t(KU) * kSortTpb) {
     int kk[KU];
@@ -162,6 +142,7 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
     for (int j = 0; j < KU; ++j) {
       const int64_t i = i0 + int64_t(j) * kSortTpb + tid;
       kk[j]           = i < n ? static_cast<int>(wkeys[i]) : -1;
+      if (unsigned(kk[j]) >= unsigned(nkeys)) kk[j] = -1;  // a key outside [0, nkeys) drops its row
     }
 #pragma unroll
     for (int j = 0; j < KU; ++j) {
@@ -182,64 +163,209 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
   }
 }
 
+// gcnt[g][k] = rows of key k in the windows of group g.
+__global__ void __launch_bounds__(256) rbk_count_kernel(const int* __restrict__ offs,
+                                                       int nkeys,
+                                                       int n_windows,
+                                                       int group,
+                                                       int n_groups,
+                                                       int* __restrict__ gcnt)
+{
+  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= int64_t(n_groups) * nkeys) return;
+  const int g  = int(idx / nkeys);
+  const int k  = int(idx - int64_t(g) * nkeys);
+  const int w0 = g * group;
+  int nw       = n_windows - w0;
+  nw           = nw < group ? nw : group;
+  int t        = 0;
+  for (int w = 0; w < nw; ++w) {
+    const int* wo = offs + size_t(w0 + w) * (nkeys + 1);
+    t += wo[k + 1] - wo[k];
+  }
+  gcnt[idx] = t;
+}
+
+// One CTA per group. From gcnt[g][.], keys taken TPB at a time so that loads and stores coalesce:
+//   uoffs[g][nkeys + 1]            first work unit of each key
+//   ukey / ufirst / ulen [max_units]  per unit: key, ordinal of its first row among the key's rows
+//                                  of the group, and row count (an even split into
+//                                  ceil(rows / kUnitCap) units)
+//   fold_list                      (g * nkeys + k) of every key that got more than one unit
+template <int TPB>
+__global__ void __launch_bounds__(TPB) rbk_units_kernel(const int* __restrict__ gcnt,
+                                                       int nkeys,
+                                                       int max_units,
+                                                       int* __restrict__ uoffs,
+                                                       int* __restrict__ ukey,
+                                                       int* __restrict__ ufirst,
+                                                       int* __restrict__ ulen,
+                                                       int* __restrict__ fold_list,
+                                                       int* __restrict__ fold_count)
+{
+  static_assert(TPB / 32 <= 32, "one warp scans the warp totals");
+  __shared__ int s_warp[TPB / 32];
+  __shared__ int s_total;
+  const int g    = blockIdx.x;
+  const int tid  = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int* cnt = gcnt + size_t(g) * nkeys;
+  int* g_uoffs   = uoffs + size_t(g) * (nkeys + 1);
+  int* g_ukey    = ukey + size_t(g) * max_units;
+  int* g_ufirst  = ufirst + size_t(g) * max_units;
+  int* g_ulen    = ulen + size_t(g) * max_units;
+
+  int run = 0;  // units of the keys before this tile
+  for (int k0 = 0; k0 < nkeys; k0 += TPB) {
+    const int k  = k0 + tid;
+    const int t  = k < nkeys ? cnt[k] : 0;
+    const int nu = (t + kUnitCap - 1) / kUnitCap;
+    int inc      = nu;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, inc, off);
+      if (lane >= off) inc += a;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      const int v = lane < TPB / 32 ? s_warp[lane] : 0;
+      int wi      = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, wi, off);
+        if (lane >= off) wi += a;
+      }
+      if (lane < TPB / 32) s_warp[lane] = wi - v;  // exclusive
+      if (lane == 31) s_total = wi;
+    }
+    __syncthreads();
+    const int u_first = run + s_warp[warp] + inc - nu;
+    if (k < nkeys) {
+      g_uoffs[k] = u_first;
+      if (nu > 0) {
+        const int each = t / nu, extra = t % nu;  // even split: `extra` units get one more row
+        for (int j = 0; j < nu; ++j) {
+          g_ukey[u_first + j]   = k;
+          g_ufirst[u_first + j] = j * each + (j < extra ? j : extra);
+          g_ulen[u_first + j]   = each + (j < extra ? 1 : 0);
+        }
+        if (nu > 1) fold_list[atomicAdd(fold_count, 1)] = g * nkeys + k;
+      }
+    }
+    run += s_total;
+    __syncthreads();  // s_warp and s_total are rewritten by the next tile
+  }
+  if (tid == 0) g_uoffs[nkeys] = run;
+}
+
+// One warp per work unit; units are handed out through a global counter (zeroed by the sort
+// kernel), in (group, key) order, so that the warps finish within one unit of each other.
+//
+// The unit's rows are ordinals [first, first + len) in the concatenation, over the group's
+// windows, of the key's segments of the sorted windows. Lane j holds the segment of window j
+// (start and inclusive running count); an ordinal finds its window by a five-step search over the
+// lanes' running counts (shuffles), then its row through the window's sorted list. With eight or
+// more lanes per row the warp translates 32 ordinals at once, one per lane, and hands the row
+// numbers out by shuffle; narrower matrices translate per load.
 template <typename DataT, typename WeightT, typename SumT, int VEC>
 __global__ void __launch_bounds__(256) rbk_stream_kernel(typename sum_state<SumT>::type::carry_t* __restrict__ partial,
                                                         const DataT* __restrict__ A,
                                                         int64_t lda,
                                                         const WeightT* __restrict__ weights,
-                                                        int64_t nrows,
                                                         int ncols,
                                                         int nkeys,
                                                         int W,
                                                         int n_windows,
+                                                        int group,
+                                                        int n_groups,
                                                         int max_units,
                                                         int G,
                                                         const unsigned* __restrict__ perm,
+                                                        const int* __restrict__ offs,
                                                         const int* __restrict__ uoffs,
-                                                        const int* __restrict__ ubeg,
-                                                        const int* __restrict__ ulen)
+                                                        const int* __restrict__ ukey,
+                                                        const int* __restrict__ ufirst,
+                                                        const int* __restrict__ ulen,
+                                                        int* __restrict__ unit_counter)
 {
   using State     = typename sum_state<SumT>::type;
   using CarryT    = typename State::carry_t;
-  constexpr int Q = 8;
+  constexpr int Q = 8;  // row loads in flight per lane
   const op::Add add{};
-  const int lane  = threadIdx.x & 31;
-  const int lig   = lane & (G - 1);
-  const int grp   = lane / G;
-  const int gpw   = 32 / G;
-  const int nvec  = ncols / VEC;
-  const int64_t total_slots = int64_t(n_windows) * max_units;
-  const int64_t warps       = int64_t(gridDim.x) * 8;
-  for (int64_t slot = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5); slot < total_slots; slot += warps) {
-    const int win = int(slot / max_units);
-    const int u   = int(slot - int64_t(win) * max_units);
-    if (u >= uoffs[size_t(win) * (nkeys + 1) + nkeys]) continue;  // this window has fewer units
-    const int beg         = ubeg[slot];
-    const int len         = ulen[slot];
-    const int64_t row0    = int64_t(win) * W;
-    const unsigned* uperm = perm + row0 + beg;
-    CarryT* dst           = partial + size_t(slot) * ncols;
+  const int lane = threadIdx.x & 31;
+  const int lg   = 31 - __clz(G);
+  const int lig  = lane & (G - 1);
+  const int grp  = lane >> lg;
+  const int gpw  = 32 >> lg;
+  const int nvec = ncols / VEC;  // VEC divides ncols on the vector path
+  const int64_t total_slots = int64_t(n_groups) * max_units;
+  while (true) {
+    long long slot = 0;
+    if (lane == 0) slot = atomicAdd(unit_counter, 1);
+    slot = __shfl_sync(0xffffffffu, slot, 0);
+    if (slot >= total_slots) break;
+    const int g = int(slot / max_units);
+    const int u = int(slot - int64_t(g) * max_units);
+    if (u >= uoffs[size_t(g) * (nkeys + 1) + nkeys]) continue;  // this group has fewer units
+    const int key   = ukey[slot];
+    const int first = ufirst[slot];
+    const int len   = ulen[slot];
+    const int w0    = g * group;
+    int nw          = n_windows - w0;
+    nw              = nw < group ? nw : group;
+    int my_beg = 0, my_cnt = 0;
+    if (lane < nw) {
+      const int* wo = offs + size_t(w0 + lane) * (nkeys + 1);
+      my_beg        = wo[key];
+      my_cnt        = wo[key + 1] - my_beg;
+    }
+    int my_end = my_cnt;  // rows of the key in windows 0..lane of the group
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, my_end, off);
+      if (lane >= off) my_end += a;
+    }
+    const int64_t grow0   = int64_t(w0) * W;  // first matrix row of the group
+    const unsigned* gperm = perm + grow0;
+    // row (relative to grow0) of the unit's i-th row; every lane must call it (shuffles inside)
+    auto translate = [&](int i) -> unsigned {
+      const int o = first + (i < len ? i : len - 1);
+      int lo      = 0;  // first window whose running count exceeds o
+#pragma unroll
+      for (int step = 16; step > 0; step >>= 1) {
+        const int probe = __shfl_sync(0xffffffffu, my_end, lo + step - 1);
+        if (probe <= o) lo += step;
+      }
+      const int w_end = __shfl_sync(0xffffffffu, my_end, lo);
+      const int w_cnt = __shfl_sync(0xffffffffu, my_cnt, lo);
+      const int w_beg = __shfl_sync(0xffffffffu, my_beg, lo);
+      const unsigned in_win = unsigned(lo) * unsigned(W);
+      return in_win + gperm[in_win + unsigned(w_beg + (o - (w_end - w_cnt)))];
+    };
+    CarryT* dst = partial + size_t(slot) * ncols;
     for (int cv0 = 0; cv0 < nvec; cv0 += G) {
       const int cv      = cv0 + lig;
       const bool col_ok = cv < nvec;
+      const DataT* col  = A + grow0 * lda + int64_t(col_ok ? cv : 0) * VEC;
       State acc[VEC];
 #pragma unroll
       for (int e = 0; e < VEC; ++e)
         acc[e].init(SumT(0));
-      for (int i0 = 0; i0 < len; i0 += Q * gpw) {
+      // one pass of Q loads per lane: rows i0 + k * gpw + grp, k = 0..Q-1, taken from `row_of(k)`
+      auto pass = [&](int i0, int limit, auto row_of) {
         VecOf<DataT, VEC> v[Q];
         SumT w[Q];
 #pragma unroll
         for (int k = 0; k < Q; ++k) {
-          int i           = i0 + k * gpw + grp;
-          i               = i < len ? i : len - 1;  // duplicate, masked below
-          const int64_t r = row0 + uperm[i];
-          v[k]            = load_stream<DataT, VEC>(A + r * lda + int64_t(col_ok ? cv : 0) * VEC);
-          w[k]            = weights != nullptr ? SumT(weights[r]) : SumT(1);
+          const int64_t r = int64_t(row_of(k));
+          v[k]            = load_stream<DataT, VEC>(col + r * lda);
+          w[k]            = weights != nullptr ? SumT(weights[grow0 + r]) : SumT(1);
         }
 #pragma unroll
         for (int k = 0; k < Q; ++k) {
-          if (i0 + k * gpw + grp < len) {
+          if (i0 + k * gpw + grp < limit) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
               SumT x = SumT(v[k].e[e]);
@@ -248,6 +374,17 @@ __global__ void __launch_bounds__(256) rbk_stream_kernel(typename sum_state<SumT
             }
           }
         }
+      };
+      if (G >= 8) {  // Q * gpw divides 32: translate 32 rows, then hand them out
+        for (int tb = 0; tb < len; tb += 32) {
+          const unsigned my_row = translate(tb + lane);
+          const int nb          = len - tb < 32 ? len - tb : 32;
+          for (int i0 = 0; i0 < nb; i0 += Q * gpw)
+            pass(i0, nb, [&](int k) { return __shfl_sync(0xffffffffu, my_row, i0 + k * gpw + grp); });
+        }
+      } else {
+        for (int i0 = 0; i0 < len; i0 += Q * gpw)
+          pass(i0, len, [&](int k) { return translate(i0 + k * gpw + grp); });
       }
       // fold the row groups of the warp (they hold different rows of the same columns)
       for (int off = G; off < 32; off <<= 1) {
@@ -266,16 +403,78 @@ __global__ void __launch_bounds__(256) rbk_stream_kernel(typename sum_state<SumT
   }
 }
 
-// One CTA per key: warp j folds the key's partial rows of windows j, j+8, ... (lanes over the
-// columns, unit rows loaded four at a time), then the eight warps are folded in order through
-// shared memory. Also derives the key's row count from the sort offsets.
+// One warp per (group, key) that owns more than one work unit (the units kernel lists them):
+// folds the units' partial rows, in unit order and eight rows in flight, into the FIRST of them,
+// so that the final merge reads one row per group and key however many rows a key has (a single
+// key may own most of the matrix).
 template <typename SumT>
+__global__ void __launch_bounds__(256) rbk_fold_kernel(typename sum_state<SumT>::type::carry_t* __restrict__ partial,
+                                                      const int* __restrict__ uoffs,
+                                                      const int* __restrict__ fold_list,
+                                                      const int* __restrict__ fold_count,
+                                                      int max_units,
+                                                      int ncols,
+                                                      int nkeys)
+{
+  using State  = typename sum_state<SumT>::type;
+  using CarryT = typename State::carry_t;
+  constexpr int R = 8;
+  const op::Add add{};
+  const int lane  = threadIdx.x & 31;
+  const int n     = *fold_count;
+  for (int idx = blockIdx.x * 8 + (threadIdx.x >> 5); idx < n; idx += gridDim.x * 8) {
+    const int gk  = fold_list[idx];
+    const int g   = gk / nkeys;
+    const int k   = gk - g * nkeys;
+    const int* gu = uoffs + size_t(g) * (nkeys + 1);
+    const int u0  = gu[k];
+    const int u1  = gu[k + 1];
+    CarryT* rows = partial + size_t(g) * max_units * ncols;
+    for (int c0 = 0; c0 < ncols; c0 += 128) {
+      State acc[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        acc[e].init(SumT(0));
+      for (int u = u0; u < u1; u += R) {
+        CarryT v[R][4];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = c0 + e * 32 + lane;
+            v[j][e]     = (u + j < u1 && c < ncols) ? rows[size_t(u + j) * ncols + c] : CarryT(0);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            acc[e].push_carry(v[j][e], add);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int c = c0 + e * 32 + lane;
+        if (c < ncols) rows[size_t(u0) * ncols + c] = acc[e].carry();
+      }
+    }
+  }
+}
+
+// WPK warps per key (8 for few keys, so that the merge has enough loads in flight; 1 otherwise).
+// Lanes run over the columns (four per lane and pass); warp s of a key folds the unit rows of
+// groups s, s + WPK, ... (one row per group after rbk_fold_kernel), four loaded before any is
+// consumed, and the WPK partial results are added in warp order through shared memory: the order
+// of the additions is fixed.
+// Warp 0 of the key also adds up the key's row count from the sort offsets of all windows.
+template <typename SumT, int WPK>
 __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
                                                        long long* __restrict__ counts,
                                                        const typename sum_state<SumT>::type::carry_t* __restrict__ partial,
                                                        const int* __restrict__ offs,
                                                        const int* __restrict__ uoffs,
                                                        int n_windows,
+                                                       int n_groups,
                                                        int max_units,
                                                        int ncols,
                                                        int nkeys,
@@ -283,48 +482,54 @@ __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
 {
   using State  = typename sum_state<SumT>::type;
   using CarryT = typename State::carry_t;
+  static_assert(WPK == 1 || WPK == 8, "one warp or one CTA per key");
+  __shared__ CarryT s_part[WPK > 1 ? WPK : 1][128];
   const op::Add add{};
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  State* s_acc     = reinterpret_cast<State*>(smem_raw);            // [8][chunk]
-  int2* s_rng      = reinterpret_cast<int2*>(s_acc + 8 * 128);      // [n_windows] unit range of key k
-  __shared__ long long s_n[8];
-  const int k      = blockIdx.x;
   const int lane   = threadIdx.x & 31;
   const int warp   = threadIdx.x >> 5;
-  constexpr int CH = 128;  // columns per pass: 4 per lane
+  const int sub    = WPK > 1 ? warp : 0;                        // this warp's share of the groups
+  const int k      = WPK > 1 ? int(blockIdx.x) : int(blockIdx.x) * 8 + warp;
+  const bool valid = k < nkeys;  // uniform per CTA when WPK > 1, so the barriers below are safe
 
-  long long n_rows_k = 0;
-  for (int w = warp * 32 + lane; w < n_windows; w += 256) {
-    const int* wo = offs + size_t(w) * (nkeys + 1);
-    const int* wu = uoffs + size_t(w) * (nkeys + 1);
-    n_rows_k += wo[k + 1] - wo[k];
-    s_rng[w] = make_int2(wu[k], wu[k + 1]);
-  }
-  __syncthreads();
+  if (valid && sub == 0 && counts != nullptr) {
+    long long n = 0;
+    for (int w = lane; w < n_windows; w += 32) {
+      const int* wo = offs + size_t(w) * (nkeys + 1);
+      n += wo[k + 1] - wo[k];
+    }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1)
-    n_rows_k += __shfl_xor_sync(0xffffffffu, n_rows_k, off);
-  if (lane == 0) s_n[warp] = n_rows_k;
+    for (int off = 16; off > 0; off >>= 1)
+      n += __shfl_xor_sync(0xffffffffu, n, off);
+    if (lane == 0) counts[k] = (reset ? 0ll : counts[k]) + n;
+  }
 
-  for (int c0 = 0; c0 < ncols; c0 += CH) {
+  for (int c0 = 0; c0 < ncols; c0 += 128) {
     State acc[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      acc[e].init(SumT(0));
-    // four windows per step: the first unit row of each (most keys have one or two units per
-    // window) is loaded before any of them is consumed, so four loads per lane are in flight
-    for (int w0 = warp; w0 < n_windows; w0 += 32) {
-      int2 rng[4];
+    for (int e = 0; e < 4; ++e) {
+      const int c = c0 + e * 32 + lane;
+      acc[e].init((!valid || sub != 0 || reset || c >= ncols) ? SumT(0) : sums[size_t(k) * ncols + c]);
+    }
+    for (int g0 = sub; valid && g0 < n_groups; g0 += 4 * WPK) {
+      int u0[4], u1[4];
       CarryT first[4][4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int w = w0 + 8 * j;
-        rng[j]      = w < n_windows ? s_rng[w] : make_int2(0, 0);
+        const int g = g0 + j * WPK;
+        u0[j] = u1[j] = 0;
+        if (g < n_groups) {
+          const int* gu = uoffs + size_t(g) * (nkeys + 1);
+          u0[j]         = gu[k];
+          u1[j]         = gu[k + 1];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = c0 + e * 32 + lane;
-          first[j][e] = (rng[j].y > rng[j].x && c < ncols)
-                          ? partial[(size_t(w) * max_units + rng[j].x) * ncols + c]
+          first[j][e] = (u1[j] > u0[j] && c < ncols)
+                          ? partial[(size_t(g0 + j * WPK) * max_units + u0[j]) * ncols + c]
                           : CarryT(0);
         }
       }
@@ -333,83 +538,122 @@ __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           acc[e].push_carry(first[j][e], add);
-        const CarryT* wpart = partial + size_t(w0 + 8 * j) * max_units * ncols;
-        for (int u = rng[j].x + 1; u < rng[j].y; ++u) {
+      }
+    }
+    if constexpr (WPK > 1) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = c0 + e * 32 + lane;
-            if (c < ncols) acc[e].push_carry(wpart[size_t(u) * ncols + c], add);
-          }
+      for (int e = 0; e < 4; ++e)
+        s_part[warp][e * 32 + lane] = acc[e].carry();
+      __syncthreads();
+      if (sub == 0) {
+        for (int s = 1; s < WPK; ++s) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            acc[e].push_carry(s_part[s][e * 32 + lane], add);
         }
       }
+      __syncthreads();
     }
+    if (valid && sub == 0) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      s_acc[warp * CH + e * 32 + lane] = acc[e];
-    __syncthreads();
-    if (threadIdx.x < CH) {
-      const int c = c0 + threadIdx.x;
-      if (c < ncols) {
-        State t;
-        t.init(reset ? SumT(0) : sums[size_t(k) * ncols + c]);
-        for (int j = 0; j < 8; ++j)
-          t.merge(s_acc[j * CH + threadIdx.x], add);
-        sums[size_t(k) * ncols + c] = t.value();
+      for (int e = 0; e < 4; ++e) {
+        const int c = c0 + e * 32 + lane;
+        if (c < ncols) sums[size_t(k) * ncols + c] = acc[e].value();
       }
     }
-    __syncthreads();
   }
-  if (counts != nullptr && threadIdx.x == 0) {
-    long long n = reset ? 0ll : counts[k];
-    for (int j = 0; j < 8; ++j)
-      n += s_n[j];
-    counts[k] = n;
-  }
+}
+
+// Shared memory of one sort CTA: histogram + cursors, and the staged 16-bit permutation.
+inline size_t rbk_sort_smem(int64_t nkeys, int64_t W, bool staged)
+{
+  return size_t(nkeys) * 2 * sizeof(int) + (staged ? size_t(W) * sizeof(unsigned short) : 0);
 }
 
 template <typename DataT>
 inline SortedPlan plan_rows_by_key_sorted(const DataT* A, int64_t lda, int64_t nrows, int64_t ncols, int64_t nkeys,
-                                          size_t sum_size)
+                                          size_t carry_size)
 {
   constexpr int V16 = vec16<DataT>::value;
   SortedPlan p      = {};
   const bool vec_ok = V16 > 1 && ncols % V16 == 0 && lda % V16 == 0 && aligned16(A);
   p.vec             = vec_ok ? V16 : 1;
-  // windows: about two per SM, between 16 Ki and 128 Ki rows
-  int64_t W = int64_t(next_pow2(unsigned(ceil_div<int64_t>(nrows, int64_t(sm_count()) * 2))));
+
+  // Window size: the sort runs one CTA per window, so the windows should fill whole waves of
+  // (SMs x resident CTAs). Two CTAs of 1024 threads fit an SM when their shared memory does.
+  const int64_t sm_smem = int64_t(228) << 10;  // per SM; every CTA also reserves 1 KB
+  const int64_t fixed   = 1024 + 256;          // reserve + static shared memory
+  const int sms         = sm_count();
+  int64_t w_floor       = ceil_div<int64_t>(nkeys, 1024) * 1024;  // histogram work <= row work
+  if (w_floor < 4096) w_floor = 4096;
+  int64_t best_w = 0, best_cost = 0;
+  for (int cps = 2; cps >= 1; --cps) {
+    int64_t w_max = ((sm_smem / cps - fixed - nkeys * 8) / 2) / 1024 * 1024;
+    if (w_max > 65536) w_max = 65536;
+    if (w_max < 4096) continue;
+    const int64_t slots = int64_t(sms) * cps;
+    const int64_t waves = ceil_div<int64_t>(nrows, slots * w_max);
+    int64_t W           = ceil_div<int64_t>(ceil_div<int64_t>(nrows, waves * slots), 1024) * 1024;
+    if (W < w_floor) W = w_floor;
+    if (W > w_max) W = w_max;
+    const int64_t real_waves = ceil_div<int64_t>(ceil_div<int64_t>(nrows, W), slots);
+    const int64_t cost       = real_waves * (2 * W + nkeys) * (cps == 2 ? 4 : 3);  // co-resident CTAs share an SM
+    if (best_w == 0 || cost < best_cost) {
+      best_w    = W;
+      best_cost = cost;
+    }
+  }
+  if (best_w == 0) best_w = 65536;  // not staged (the launcher falls back to direct stores)
   const int knob = tuning().key_window_rows;
-  if (knob > 0 && (knob & (knob - 1)) == 0) W = knob;
-  if (W < 16384) W = 16384;
-  if (W > 131072) W = 131072;
-  p.window_rows = int(W);
-  p.n_windows   = int(ceil_div<int64_t>(nrows, W));
-  const int64_t rows_in_win = nrows < W ? nrows : W;
-  int64_t mu    = nkeys + rows_in_win / kUnitRows;  // every key may have one ragged unit
-  if (mu > rows_in_win) mu = rows_in_win;           // a unit holds at least one row
-  if (mu < 1) mu = 1;
-  p.max_units   = int(mu);
-  size_t o      = 0;
-  p.off_perm    = o;
+  if (knob >= 1024 && knob <= 65536) best_w = knob;
+  const int64_t W    = best_w;
+  p.window_rows      = int(W);
+  p.n_windows        = int(ceil_div<int64_t>(nrows, W));
+  // windows per group: a key should own about kUnitTarget rows of a group
+  int64_t group = (int64_t(kUnitTarget) * nkeys + W / 2) / W;
+  if (group > kMaxGroup) group = kMaxGroup;
+  if (group > p.n_windows) group = p.n_windows;
+  if (group < 1) group = 1;
+  p.group    = int(group);
+  p.n_groups = int(ceil_div<int64_t>(p.n_windows, group));
+  const int64_t group_rows    = group * W;
+  const int64_t rows_in_group = nrows < group_rows ? nrows : group_rows;
+  // every key present adds at most one ragged unit on top of the full ones
+  const int64_t present = nkeys < rows_in_group ? nkeys : rows_in_group;
+  p.max_units           = int(present + rows_in_group / kUnitCap + 1);
+  const int64_t heavy   = rows_in_group / kUnitCap + 1;  // keys with more than kUnitCap rows in a group
+  p.max_fold            = int(int64_t(p.n_groups) * (heavy < nkeys ? heavy : nkeys));
+  const size_t per_key  = size_t(nkeys + 1) * sizeof(int);
+  const size_t per_unit = size_t(p.n_groups) * p.max_units * sizeof(int);
+  size_t o              = 0;
+  p.off_perm            = o;
   o += align_up(size_t(nrows) * sizeof(unsigned), 256);
   p.off_offs = o;
-  o += align_up(size_t(p.n_windows) * (nkeys + 1) * sizeof(int), 256);
+  o += align_up(size_t(p.n_windows) * per_key, 256);
+  p.off_gcnt = o;
+  o += align_up(size_t(p.n_groups) * nkeys * sizeof(int), 256);
   p.off_uoffs = o;
-  o += align_up(size_t(p.n_windows) * (nkeys + 1) * sizeof(int), 256);
+  o += align_up(size_t(p.n_groups) * per_key, 256);
   p.off_ukey = o;
-  o += align_up(size_t(p.n_windows) * p.max_units * sizeof(int), 256);
-  p.off_ubeg = o;
-  o += align_up(size_t(p.n_windows) * p.max_units * sizeof(int), 256);
+  o += align_up(per_unit, 256);
+  p.off_ufirst = o;
+  o += align_up(per_unit, 256);
   p.off_ulen = o;
-  o += align_up(size_t(p.n_windows) * p.max_units * sizeof(int), 256);
+  o += align_up(per_unit, 256);
+  p.off_fold = o;
+  o += align_up(size_t(p.max_fold) * sizeof(int), 256);
+  p.off_counter = o;
+  o += 256;
   p.off_part = o;
-  o += align_up(size_t(p.n_windows) * p.max_units * size_t(ncols) * sum_size, 256);
+  o += align_up(size_t(p.n_groups) * p.max_units * size_t(ncols) * carry_size, 256);
   p.total = o;
   return p;
 }
 
+// The unit queue is a 32-bit counter and offsets inside a group are 32-bit: 2^30 rows at most.
 inline bool rows_by_key_sorted_supported(int64_t nrows, int64_t ncols, int64_t nkeys)
 {
-  return nkeys <= kMaxSortKeys && ncols <= int64_t(0x7fffffff) && nrows > 0;
+  return nkeys <= kMaxSortKeys && ncols <= int64_t(0x7fffffff) && nrows > 0 && nrows <= (int64_t(1) << 30);
 }
 
 template <typename DataT, typename KeyT, typename WeightT, typename SumT>
@@ -434,41 +678,55 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   unsigned char* base = static_cast<unsigned char*>(scratch.get());
   unsigned* perm      = reinterpret_cast<unsigned*>(base + p.off_perm);
   int* offs           = reinterpret_cast<int*>(base + p.off_offs);
+  int* gcnt           = reinterpret_cast<int*>(base + p.off_gcnt);
   int* uoffs          = reinterpret_cast<int*>(base + p.off_uoffs);
   int* ukey           = reinterpret_cast<int*>(base + p.off_ukey);
-  int* ubeg           = reinterpret_cast<int*>(base + p.off_ubeg);
+  int* ufirst         = reinterpret_cast<int*>(base + p.off_ufirst);
   int* ulen           = reinterpret_cast<int*>(base + p.off_ulen);
+  int* fold_list      = reinterpret_cast<int*>(base + p.off_fold);
+  int* counter        = reinterpret_cast<int*>(base + p.off_counter);  // [0] unit queue, [1] fold list length
   CarryT* partial     = reinterpret_cast<CarryT*>(base + p.off_part);
+  const int nk        = int(nkeys);
+  const int sms       = sm_count();
   cudaError_t e;
 
-  const size_t hist_smem   = size_t(nkeys) * 2 * sizeof(int);
-  const size_t staged_smem = hist_smem + size_t(p.window_rows) * sizeof(unsigned short);
-  const bool staged        = p.window_rows <= 65536 && staged_smem <= (size_t(220) << 10);
-  const size_t sort_smem   = staged ? staged_smem : hist_smem;
-  auto sort_kern           = staged ? rbk_sort_kernel<KeyT, true> : rbk_sort_kernel<KeyT, false>;
+  // 1. per-window counting sort
+  const size_t smem_cap  = (size_t(227) << 10) - 256;  // most a CTA may opt into, less the static part
+  const bool staged      = rbk_sort_smem(nkeys, p.window_rows, true) <= smem_cap;
+  const size_t sort_smem = rbk_sort_smem(nkeys, p.window_rows, staged);
+  auto sort_kern         = staged ? rbk_sort_kernel<KeyT, true> : rbk_sort_kernel<KeyT, false>;
   if (sort_smem + 1024 > (size_t(48) << 10)) {  // static shared memory counts against the 48 KB too
     e = cudaFuncSetAttribute(sort_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sort_smem));
     if (e != cudaSuccess) return e;
   }
-  sort_kern<<<unsigned(p.n_windows), kSortTpb, sort_smem, stream>>>(
-    keys, nrows, int(nkeys), p.window_rows, p.max_units, perm, offs, uoffs, ukey, ubeg, ulen);
+  sort_kern<<<unsigned(p.n_windows), kSortTpb, sort_smem, stream>>>(keys, nrows, nk, p.window_rows, perm, offs,
+                                                                    counter);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
-  const int nvec           = int(ncols / p.vec);
-  unsigned g               = next_pow2(unsigned(nvec > 0 ? nvec : 1));
-  const int G              = int(g > 32u ? 32u : g);
-  const int64_t slots      = int64_t(p.n_windows) * p.max_units;
-  const int sms            = sm_count();
-#define B2R_LAUNCH_STREAM(VEC_)                                                                        \
-  do {                                                                                                 \
-    auto kern      = rbk_stream_kernel<DataT, WeightT, SumT, VEC_>;                                    \
-    static int occ = resident_ctas(kern, 256, 0);                                                      \
-    int64_t ctas   = int64_t(sms) * occ;                                                               \
-    if (ctas > ceil_div<int64_t>(slots, 8)) ctas = ceil_div<int64_t>(slots, 8);                        \
-    kern<<<unsigned(ctas), 256, 0, stream>>>(partial, A, lda, weights, nrows, int(ncols), int(nkeys),  \
-                                             p.window_rows, p.n_windows, p.max_units, G, perm, uoffs,  \
-                                             ubeg, ulen);                                              \
+  // 2. rows per (group, key); 3. unit tables and the list of keys to fold
+  const int64_t gk = int64_t(p.n_groups) * nkeys;
+  rbk_count_kernel<<<unsigned(ceil_div<int64_t>(gk, 256)), 256, 0, stream>>>(offs, nk, p.n_windows, p.group,
+                                                                             p.n_groups, gcnt);
+  rbk_units_kernel<1024><<<unsigned(p.n_groups), 1024, 0, stream>>>(gcnt, nk, p.max_units, uoffs, ukey, ufirst, ulen,
+                                                                    fold_list, counter + 1);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+
+  // 4. stream the matrix, one warp per unit
+  const int nvec      = int(ncols / p.vec);
+  const unsigned g    = next_pow2(unsigned(nvec > 0 ? nvec : 1));
+  const int G         = int(g > 32u ? 32u : g);
+  const int64_t slots = int64_t(p.n_groups) * p.max_units;
+#define B2R_LAUNCH_STREAM(VEC_)                                                                              \
+  do {                                                                                                       \
+    auto kern      = rbk_stream_kernel<DataT, WeightT, SumT, VEC_>;                                          \
+    static int occ = resident_ctas(kern, 256, 0);                                                            \
+    int64_t ctas   = int64_t(sms) * occ;                                                                     \
+    if (ctas > ceil_div<int64_t>(slots, 8)) ctas = ceil_div<int64_t>(slots, 8);                              \
+    kern<<<unsigned(ctas), 256, 0, stream>>>(partial, A, lda, weights, int(ncols), nk, p.window_rows,        \
+                                             p.n_windows, p.group, p.n_groups, p.max_units, G, perm, offs,   \
+                                             uoffs, ukey, ufirst, ulen, counter);                            \
   } while (0)
   if (p.vec > 1) {
     B2R_LAUNCH_STREAM(V16);
@@ -479,14 +737,19 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
-  const size_t merge_smem =
-    size_t(8) * 128 * sizeof(typename sum_state<SumT>::type) + size_t(p.n_windows) * sizeof(int2);
-  if (merge_smem + 1024 > (size_t(48) << 10)) {
-    e = cudaFuncSetAttribute(rbk_merge_kernel<SumT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(merge_smem));
-    if (e != cudaSuccess) return e;
+  // 5. one partial row per (group, key); 6. fold the groups of every key
+  int64_t fold_ctas = ceil_div<int64_t>(p.max_fold, 8);
+  if (fold_ctas > int64_t(sms) * 8) fold_ctas = int64_t(sms) * 8;
+  if (fold_ctas < 1) fold_ctas = 1;
+  rbk_fold_kernel<SumT><<<unsigned(fold_ctas), 256, 0, stream>>>(partial, uoffs, fold_list, counter + 1, p.max_units,
+                                                                 int(ncols), nk);
+  if (nkeys <= 2048) {  // few keys: a CTA per key
+    rbk_merge_kernel<SumT, 8><<<unsigned(nkeys), 256, 0, stream>>>(
+      sums, counts, partial, offs, uoffs, p.n_windows, p.n_groups, p.max_units, int(ncols), nk, reset);
+  } else {
+    rbk_merge_kernel<SumT, 1><<<unsigned(ceil_div<int64_t>(nkeys, 8)), 256, 0, stream>>>(
+      sums, counts, partial, offs, uoffs, p.n_windows, p.n_groups, p.max_units, int(ncols), nk, reset);
   }
-  rbk_merge_kernel<SumT><<<unsigned(nkeys), 256, merge_smem, stream>>>(
-    sums, counts, partial, offs, uoffs, p.n_windows, p.max_units, int(ncols), int(nkeys), reset);
   return cudaGetLastError();
 }
 

@@ -20,6 +20,10 @@ pytestmark = pytest.mark.gpu
     (20000, 128, 1024, np.float32, 1e-5),
     (5000, 4, 7, np.float32, 1e-5),
     (3000, 130, 300, np.float64, 1e-9),
+    (300000, 64, 1024, np.float32, 1e-5),    # several groups of several windows, ragged last group
+    (300000, 16, 16384, np.float32, 1e-5),   # one group of 19 windows, about 18 rows per key
+    (70000, 32, 24576, np.float32, 1e-5),    # most keys the sorted path takes
+    (70000, 32, 30000, np.float32, 1e-5),    # beyond it: shared-memory table slices
 ])
 @pytest.mark.parametrize("weighted", [False, True])
 @pytest.mark.parametrize("key_dt", [np.int32, np.int64])
