@@ -202,6 +202,22 @@ B2R_API int b2r_reduce_cols_by_key(void* out,
                                    b2r_stream_t stream);
 
 /*
+ * raft::linalg::row_normalize<norm_type> - linalg/normalize.cuh:88-107, kernels
+ * linalg/detail/normalize.cuh:26-197: every row of a row-major [n_rows x n_cols] matrix is divided
+ * by its L1 / L2 (with root) / Linf norm; a row whose norm is <= eps is NOT written (out keeps its
+ * previous content there), as in the reference. dtype: B2R_F32 or B2R_F64 (input and output).
+ * `out` may be `in`. One pass: every element is read once and written once.
+ */
+B2R_API int b2r_row_normalize(void* out,
+                              const void* in,
+                              int32_t dtype,
+                              int64_t n_rows,
+                              int64_t n_cols,
+                              int32_t norm_type,
+                              double eps,
+                              b2r_stream_t stream);
+
+/*
  * raft::matrix::argmin / argmax - matrix/argmin.cuh:27-39, matrix/argmax.cuh:27-39, kernel
  * matrix/detail/math.cuh:291-352: out[r] = column index of the smallest / largest element of row r
  * of a row-major [n_rows x n_cols] matrix; on equal values the lowest index wins (cub::ArgMin /

@@ -147,6 +147,14 @@ struct KeyOf {
 };
 
 // Final op chosen at run time (it runs once per output, so a switch costs nothing).
+struct Sqrt {
+  template <typename T, typename... I>
+  B2R_HDI T operator()(const T& x, I...) const
+  {
+    return T(sqrt(x));
+  }
+};
+
 enum FinalKind : int { kFinIdentity = 0, kFinSqrt = 1, kFinMulConst = 2, kFinDivConst = 3, kFinAbs = 4 };
 
 template <typename T>

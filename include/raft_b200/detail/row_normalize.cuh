@@ -1,0 +1,237 @@
+// Row normalisation: out[i][:] = in[i][:] / norm_i with norm_i = final(reduce_j main(in[i][j], j)),
+// rows whose norm is <= eps are left untouched in `out`
+// (raft::linalg::row_normalize, linalg/normalize.cuh:46-107, kernels linalg/detail/normalize.cuh:26-197).
+//
+// Read-reduce-rescale in ONE pass over HBM: 2 x sizeof(T) bytes per element.
+//
+//  row_normalize_kernel       rows of up to 256 16-byte vectors (1024 fp32): a sub-warp of G lanes
+//                             holds the whole row in registers (CPL vectors per lane), U rows at a
+//                             time so that 8 loads are in flight per lane; butterfly reduction, then
+//                             the same registers are divided and stored.
+//  row_normalize_long_kernel  longer rows: one CTA per row, two sweeps; the second sweep re-reads the
+//                             row from L1 / L2 (it was just touched), so DRAM still sees it once.
+#pragma once
+
+#include "common.cuh"
+#include "launch.cuh"
+#include "ops.cuh"
+
+namespace raft_b200 {
+namespace detail {
+
+template <typename T, int VEC>
+B2R_DI void store_vec(T* p, const VecOf<T, VEC>& v)
+{
+  *reinterpret_cast<VecOf<T, VEC>*>(p) = v;
+}
+
+template <typename T, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp, int VEC, int CPL, int U>
+__global__ void __launch_bounds__(256) row_normalize_kernel(T* out,
+                                                           const T* in,
+                                                           int64_t n_rows,
+                                                           int64_t n_cols,
+                                                           T init,
+                                                           T eps,
+                                                           MainOp main_op,
+                                                           ReduceOp reduce_op,
+                                                           FinalOp final_op,
+                                                           int G)
+{
+  using State = typename state_for<T, ReduceOp>::type;
+  const int lane = threadIdx.x & 31;
+  const int lg   = 31 - __clz(G);
+  const int lig  = lane & (G - 1);
+  const int grp  = lane >> lg;
+  const int gpw  = 32 >> lg;              // rows per warp and load
+  const int nvec = int(n_cols / VEC);     // VEC divides n_cols on the vector path
+  const int64_t rows_per_pass = int64_t(gpw) * U;
+  const int64_t warp0         = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n_warps       = int64_t(gridDim.x) * (blockDim.x >> 5);
+  bool chunk_ok[CPL];
+#pragma unroll
+  for (int k = 0; k < CPL; ++k)
+    chunk_ok[k] = k * G + lig < nvec;
+
+  for (int64_t r0 = warp0 * rows_per_pass; r0 < n_rows; r0 += n_warps * rows_per_pass) {
+    VecOf<T, VEC> v[U][CPL];
+    bool row_ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t r  = r0 + int64_t(u) * gpw + grp;
+      row_ok[u]        = r < n_rows;
+      const T* row_ptr = in + (row_ok[u] ? r : r0) * n_cols;
+#pragma unroll
+      for (int k = 0; k < CPL; ++k)
+        v[u][k] = load_stream<T, VEC>(row_ptr + int64_t(chunk_ok[k] ? k * G + lig : 0) * VEC);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      State st;
+      st.init(init);
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) {
+        if (chunk_ok[k]) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            st.push(T(main_op(v[u][k].e[e], IdxT((k * G + lig) * VEC + e))), reduce_op);
+        }
+      }
+      for (int off = G >> 1; off > 0; off >>= 1) {
+        State got = shfl_xor_any(st, off);
+        st.merge(got, reduce_op);
+      }
+      // every lane of the row divides by the SAME value: the one of the group's first lane
+      const T norm = shfl_idx_any(T(final_op(st.value())), lane & ~(G - 1));
+      if (row_ok[u] && !(norm <= eps)) {
+        T* row_ptr = out + (r0 + int64_t(u) * gpw + grp) * n_cols;
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+          if (chunk_ok[k]) {
+            VecOf<T, VEC> o;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              o.e[e] = v[u][k].e[e] / norm;
+            store_vec<T, VEC>(row_ptr + int64_t(k * G + lig) * VEC, o);
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename T, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp, int VEC>
+__global__ void __launch_bounds__(256) row_normalize_long_kernel(T* out,
+                                                                const T* in,
+                                                                int64_t n_rows,
+                                                                int64_t n_cols,
+                                                                T init,
+                                                                T eps,
+                                                                MainOp main_op,
+                                                                ReduceOp reduce_op,
+                                                                FinalOp final_op)
+{
+  using State     = typename state_for<T, ReduceOp>::type;
+  using Vec       = VecOf<T, VEC>;
+  constexpr int Q = 4;  // loads in flight per thread
+  __shared__ State s_state[8];
+  __shared__ T s_norm;
+  const int tid      = threadIdx.x;
+  const int64_t nvec = n_cols / VEC;
+  for (int64_t r = blockIdx.x; r < n_rows; r += gridDim.x) {
+    const T* src = in + r * n_cols;
+    State st;
+    st.init(init);
+    for (int64_t c0 = tid; c0 < nvec; c0 += int64_t(Q) * 256) {
+      Vec v[Q];
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        const int64_t c = c0 + int64_t(q) * 256;
+        v[q]            = *reinterpret_cast<const Vec*>(src + (c < nvec ? c : c0) * VEC);  // cached: read again below
+      }
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        const int64_t c = c0 + int64_t(q) * 256;
+        if (c < nvec) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            st.push(T(main_op(v[q].e[e], IdxT(c * VEC + e))), reduce_op);
+        }
+      }
+    }
+    st = block_merge(st, reduce_op, s_state);
+    if (tid == 0) s_norm = T(final_op(st.value()));
+    __syncthreads();
+    const T norm = s_norm;
+    if (!(norm <= eps)) {
+      T* dst = out + r * n_cols;
+      for (int64_t c0 = tid; c0 < nvec; c0 += int64_t(Q) * 256) {
+        Vec v[Q];
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+          const int64_t c = c0 + int64_t(q) * 256;
+          v[q]            = *reinterpret_cast<const Vec*>(src + (c < nvec ? c : c0) * VEC);
+        }
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+          const int64_t c = c0 + int64_t(q) * 256;
+          if (c < nvec) {
+            Vec o;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              o.e[e] = v[q].e[e] / norm;
+            store_vec<T, VEC>(dst + c * VEC, o);
+          }
+        }
+      }
+    }
+    __syncthreads();  // s_state / s_norm are rewritten for the next row
+  }
+}
+
+// Rows of up to kNormRegVecs vectors stay in registers.
+constexpr int kNormRegVecs = 256;
+
+template <typename T, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp>
+cudaError_t launch_row_normalize(T* out,
+                                 const T* in,
+                                 int64_t n_rows,
+                                 int64_t n_cols,
+                                 T init,
+                                 T eps,
+                                 MainOp main_op,
+                                 ReduceOp reduce_op,
+                                 FinalOp final_op,
+                                 cudaStream_t stream)
+{
+  if (n_rows <= 0 || n_cols <= 0) return cudaSuccess;
+  constexpr int V16 = vec16<T>::value;
+  const bool vec_ok = V16 > 1 && n_cols % V16 == 0 && aligned16(in) && aligned16(out);
+  const int vec     = vec_ok ? V16 : 1;
+  const int64_t nvec = n_cols / vec;
+  const int sms      = sm_count();
+
+#define B2R_NORMALIZE_REG(VEC_, CPL_)                                                                     \
+  do {                                                                                                    \
+    constexpr int U_ = 8 / CPL_;                                                                          \
+    auto kern        = row_normalize_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_, CPL_, U_>;          \
+    static int occ   = resident_ctas(kern, 256, 0);                                                       \
+    const unsigned g = next_pow2(unsigned(ceil_div<int64_t>(nvec, CPL_)));                                \
+    const int G      = int(g > 32u ? 32u : g);                                                            \
+    const int64_t rows_per_cta = int64_t(32 / G) * U_ * 8;                                                \
+    int64_t ctas               = ceil_div<int64_t>(n_rows, rows_per_cta);                                 \
+    const int64_t cap          = int64_t(sms) * occ * 2;                                                  \
+    if (ctas > cap) ctas = cap;                                                                           \
+    kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,      \
+                                             final_op, G);                                                \
+  } while (0)
+#define B2R_NORMALIZE_ANY(VEC_)                                                                           \
+  do {                                                                                                    \
+    if (nvec > kNormRegVecs) {                                                                            \
+      auto kern      = row_normalize_long_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_>;               \
+      static int occ = resident_ctas(kern, 256, 0);                                                       \
+      int64_t ctas   = n_rows;                                                                            \
+      if (ctas > int64_t(sms) * occ) ctas = int64_t(sms) * occ;                                           \
+      kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,    \
+                                               final_op);                                                 \
+    } else if (nvec > 128) {                                                                              \
+      B2R_NORMALIZE_REG(VEC_, 8);                                                                         \
+    } else if (nvec >= 32) {                                                                              \
+      B2R_NORMALIZE_REG(VEC_, 4);                                                                         \
+    } else if (nvec >= 8) {                                                                               \
+      B2R_NORMALIZE_REG(VEC_, 2);                                                                         \
+    } else {                                                                                              \
+      B2R_NORMALIZE_REG(VEC_, 1);                                                                         \
+    }                                                                                                     \
+  } while (0)
+  if (vec > 1) {
+    B2R_NORMALIZE_ANY(V16);
+  } else {
+    B2R_NORMALIZE_ANY(1);
+  }
+#undef B2R_NORMALIZE_ANY
+#undef B2R_NORMALIZE_REG
+  return cudaGetLastError();
+}
+
+}  // namespace detail
+}  // namespace raft_b200

@@ -29,11 +29,14 @@ FLAGS=(-std=c++20 --expt-extended-lambda --expt-relaxed-constexpr -gencode arch=
        -I"$HERE/ref_shim" -I"$CCCL/libcudacxx/include" -I"$CCCL/cub" -I"$CCCL/thrust"
        -I"$REF/cpp/include" -I"$HERE/../include")
 pids=()
-for tu in ref_reduce_rows ref_reduce_cols ref_bykey_kvp; do
+TUS=(ref_reduce_rows ref_reduce_cols ref_bykey_kvp ref_normalize)
+for tu in "${TUS[@]}"; do
   if [ "$OUT/$tu.o" -nt "$HERE/$tu.cu" ] && [ "$OUT/$tu.o" -nt "$HERE/ref_common.cuh" ]; then continue; fi
   nvcc "${FLAGS[@]}" -c "$HERE/$tu.cu" -o "$OUT/$tu.o" &
   pids+=($!)
 done
 for p in "${pids[@]:-}"; do [ -n "$p" ] && wait "$p"; done
-nvcc -gencode arch=compute_100a,code=sm_100a -shared -o "$OUT/libraft_ref.so" "$OUT"/ref_reduce_rows.o "$OUT"/ref_reduce_cols.o "$OUT"/ref_bykey_kvp.o
+OBJS=()
+for tu in "${TUS[@]}"; do OBJS+=("$OUT/$tu.o"); done
+nvcc -gencode arch=compute_100a,code=sm_100a -shared -o "$OUT/libraft_ref.so" "${OBJS[@]}"
 echo "build_ref: built $OUT/libraft_ref.so"

@@ -285,6 +285,47 @@ EXPORT int oracle_reduce(const void* in, int in_dtype, int layout, int apply, in
 }
 
 /* ------------------------------------------------------------------------------------ */
+/* row_normalize (linalg/normalize.cuh:46-107, kernels linalg/detail/normalize.cuh:26-56)*/
+/*   norm_i = final(reduce_j main(in[i][j])) evaluated in fp64 and rounded ONCE to the    */
+/*   element type; `if (norm <= eps) return;` leaves the row of `out` untouched; the      */
+/*   division runs in the element type. norm_type 1 = L1, 2 = L2 (with root), 3 = Linf.   */
+/* ------------------------------------------------------------------------------------ */
+EXPORT int oracle_row_normalize(const void* in, void* out, int dtype, int64_t n_rows, int64_t n_cols, int norm_type,
+                                double eps)
+{
+  if (dtype != DT_F32 && dtype != DT_F64) return 1;
+  if (norm_type < 1 || norm_type > 3) return 1;
+  const int main_op = norm_type == 2 ? MAIN_SQ : MAIN_ABS;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n_rows; ++i) {
+    double acc = 0.0, comp = 0.0;
+    for (int64_t j = 0; j < n_cols; ++j) {
+      const double v = apply_main(load_elem(in, dtype, i * n_cols + j), main_op, dtype);
+      if (norm_type == 3) {
+        acc = fmax(acc, v);
+      } else {
+        const double t = acc + v;
+        comp += fabs(acc) >= fabs(v) ? (acc - t) + v : (v - t) + acc;
+        acc = t;
+      }
+    }
+    double norm = acc + comp;
+    if (norm_type == 2) norm = sqrt(norm);
+    if (dtype == DT_F32) {
+      const float nf = (float)norm;
+      if (nf <= (float)eps) continue;
+      for (int64_t j = 0; j < n_cols; ++j)
+        ((float*)out)[i * n_cols + j] = ((const float*)in)[i * n_cols + j] / nf;
+    } else {
+      if (norm <= eps) continue;
+      for (int64_t j = 0; j < n_cols; ++j)
+        ((double*)out)[i * n_cols + j] = ((const double*)in)[i * n_cols + j] / norm;
+    }
+  }
+  return 0;
+}
+
+/* ------------------------------------------------------------------------------------ */
 /* by-key sums                                                                            */
 /* ------------------------------------------------------------------------------------ */
 static inline int64_t load_key(const void* keys, int key_dtype, int64_t i)

@@ -37,6 +37,7 @@ def load():
         lib.oracle_reduce.argtypes = [vp, i32, i32, i32, i64, i64, i32, i32, i32, dbl, dbl, i64, i32, vp, vp]
         lib.oracle_rows_by_key.argtypes = [vp, i32, i64, vp, i32, vp, i64, i64, i64, i32, vp, vp]
         lib.oracle_cols_by_key.argtypes = [vp, i32, vp, i32, i64, i64, i64, i32, vp]
+        lib.oracle_row_normalize.argtypes = [vp, vp, i32, i64, i64, i32, dbl]
         lib.oracle_compare_approx.argtypes = [vp, vp, i64, dbl, vp, vp, vp]
         lib.oracle_compare_approx.restype = i64
         lib.omp_threads.restype = i32
@@ -102,6 +103,19 @@ def cols_by_key(data, keys, nkeys, prev=None):
     out = np.zeros((nrows, nkeys), dtype=np.float64) if reset else np.array(prev, dtype=np.float64)
     rc = load().oracle_cols_by_key(_ptr(data), DT[data.dtype], _ptr(keys), DT[keys.dtype], nrows, ncols, nkeys,
                                    1 if reset else 0, _ptr(out))
+    assert rc == 0, rc
+    return out
+
+
+def row_normalize(data, norm_type="L2", eps=1e-8, prev=None):
+    """Oracle of raft::linalg::row_normalize (linalg/normalize.cuh:88-107): fp64 norm rounded once
+    to the element type, division in the element type; rows with norm <= eps keep `prev` (zeros
+    when not given)."""
+    data = np.ascontiguousarray(data)
+    out = np.zeros_like(data) if prev is None else np.array(prev, dtype=data.dtype)
+    n_rows, n_cols = data.shape
+    rc = load().oracle_row_normalize(_ptr(data), _ptr(out), DT[data.dtype], n_rows, n_cols,
+                                     {"L1": 1, "L2": 2, "Linf": 3}[norm_type], float(eps))
     assert rc == 0, rc
     return out
 

@@ -27,6 +27,7 @@ def load():
             getattr(lib, name).argtypes = [ctypes.POINTER(L.ReduceDesc), vp, vp, vp]
         lib.ref_rows_by_key.argtypes = [vp, vp, i64, vp, vp, i32, i64, i64, i64, i32, vp]
         lib.ref_cols_by_key.argtypes = [vp, vp, vp, i32, i64, i64, i64, i32, vp]
+        lib.ref_row_normalize.argtypes = [vp, vp, i32, i64, i64, i32, vp]
         _lib = lib
     return _lib
 
@@ -70,3 +71,12 @@ def cols_by_key(out, data, keys, nkeys, reset=True):
     with torch.cuda.device(data.device):
         return load().ref_cols_by_key(out.data_ptr(), data.data_ptr(), keys.data_ptr(), _DTYPES[data.dtype], nrows,
                                       ncols, nkeys, 1 if reset else 0, _stream(data.device))
+
+
+def row_normalize(out, data, norm_type):
+    """The reference's raft::linalg::row_normalize<norm_type> (default eps). norm_type: "L1", "L2", "Linf"."""
+    from raft_b200.linalg import _DTYPES, _NORM
+    n_rows, n_cols = data.shape
+    with torch.cuda.device(data.device):
+        return load().ref_row_normalize(out.data_ptr(), data.data_ptr(), _DTYPES[data.dtype], n_rows, n_cols,
+                                        _NORM[norm_type], _stream(data.device))

@@ -55,6 +55,7 @@ SIGNATURES = {
                                               _vp, _sz, _vp]),
     "b2r_reduce_rows_by_key_workspace_bytes": (_sz, [_vp, _i64, _i32, _i64, _i64, _i64]),
     "b2r_reduce_cols_by_key": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i32, _vp]),
+    "b2r_row_normalize": (ctypes.c_int, [_vp, _vp, _i32, _i64, _i64, _i32, _dbl, _vp]),
     "b2r_matrix_argmin": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _i64, _vp]),
     "b2r_matrix_argmax": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _i64, _vp]),
     "b2r_column_sum_f32_noalloc": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i32, _dbl, _vp]),

@@ -320,6 +320,35 @@ def argmax(data, out=None, index_dtype=torch.int32):
     return _matrix_arg("b2r_matrix_argmax", data, out, index_dtype)
 
 
+def row_normalize(data, norm_type="L2", out=None, eps=1e-8):
+    """raft::linalg::row_normalize<norm_type> (linalg/normalize.cuh:88-107): every row of a
+    row-major matrix divided by its L1 / L2 / Linf norm. A row whose norm is <= eps is not
+    written: `out` keeps what it held there (the reference's behaviour), so pass an initialised
+    `out` if such rows can occur. `out` may be `data`."""
+    _require_cuda(data, "data")
+    if data.dim() != 2 or not data.is_contiguous():
+        raise ValueError("Input must be contiguous")
+    if out is None:
+        out = torch.zeros_like(data)
+    _require_cuda(out, "out")
+    if not out.is_contiguous():
+        raise ValueError("Output must be contiguous")
+    if out.shape[0] != data.shape[0]:
+        raise ValueError("The number of rows of the input and output should be equal")
+    if out.shape[1] != data.shape[1]:
+        raise ValueError("The number of columns of the input and output should be equal")
+    if out.dtype != data.dtype:
+        raise ValueError("input and output must have the same element type")
+    if norm_type not in ("L1", "L2", "Linf"):
+        raise ValueError("Unsupported norm type: %s" % norm_type)
+    n_rows, n_cols = data.shape
+    with torch.cuda.device(data.device):
+        st = L.load().b2r_row_normalize(out.data_ptr(), data.data_ptr(), _DTYPES[data.dtype], n_rows, n_cols,
+                                        _NORM[norm_type], float(eps), _stream_ptr(data.device))
+    L.check(st, "b2r_row_normalize")
+    return out
+
+
 def apply_final(v, final_op, final_scalar=1.0):
     """v[i] = final_op(v[i]) in place (the deferred final step of a sharded reduction)."""
     _require_cuda(v, "v")
