@@ -1,5 +1,5 @@
 // Device matrix / vector views for the stand-alone build, on cuda::std::mdspan (reference:
-// core/mdspan_types.hpp:22-34, core/device_mdspan.hpp:84-98, 173, 223). Same names, template
+// core/mdspan_types.hpp:22-37, core/device_mdspan.hpp:76-98, 153-157, 173, 223). Same names, template
 // parameters and factory functions; the accessor is the default one.
 #pragma once
 #include <cuda/std/mdspan>
@@ -17,6 +17,9 @@ using matrix_extent = cuda::std::extents<IndexType, cuda::std::dynamic_extent, c
 template <typename IndexType>
 using vector_extent = cuda::std::extents<IndexType, cuda::std::dynamic_extent>;
 
+template <typename IndexType>
+using scalar_extent = cuda::std::extents<IndexType, 1>;
+
 template <typename T, typename Extents, typename Layout = row_major>
 using device_mdspan = cuda::std::mdspan<T, Extents, Layout>;
 
@@ -25,6 +28,15 @@ using device_matrix_view = device_mdspan<T, matrix_extent<IndexType>, Layout>;
 
 template <typename T, typename IndexType = std::uint32_t, typename Layout = row_major>
 using device_vector_view = device_mdspan<T, vector_extent<IndexType>, Layout>;
+
+template <typename T, typename IndexType = std::uint32_t>
+using device_scalar_view = device_mdspan<T, scalar_extent<IndexType>>;
+
+template <typename T, typename IndexType = std::uint32_t>
+auto make_device_scalar_view(T* ptr)
+{
+  return device_scalar_view<T, IndexType>{ptr, scalar_extent<IndexType>{}};
+}
 
 template <typename T, typename IndexType = std::uint32_t, typename Layout = row_major>
 auto make_device_matrix_view(T* ptr, IndexType n_rows, IndexType n_cols)

@@ -249,14 +249,16 @@ cudaError_t launch_row_reduce(StoreT* out,
     Scratch scratch(ws, need, stream);
     if (scratch.error() != cudaSuccess) return scratch.error();
     CarryT* partial       = static_cast<CarryT*>(scratch.get());
-    const int vec         = vec_ok ? V16 : 1;
+    // every row must start on a 16-byte boundary; a ragged row end is handled by the kernel
+    const bool vec_split  = V16 > 1 && aligned16(data) && (ld % V16 == 0 || n_rows == 1);
+    const int vec         = vec_split ? V16 : 1;
     const int64_t nvec    = row_len / vec;
     int64_t seg_vecs      = ceil_div<int64_t>(nvec, n_seg);
     seg_vecs              = ceil_div<int64_t>(seg_vecs, TPB) * TPB;
     n_seg                 = int(ceil_div<int64_t>(nvec, seg_vecs));
     if (n_seg < 1) n_seg = 1;
     const dim3 grid{unsigned(n_seg), unsigned(n_rows < 65535 ? n_rows : 65535), 1u};
-    if (vec_ok) {
+    if (vec_split) {
       row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, 4, TPB, StoreT>
         <<<grid, TPB, 0, stream>>>(
           out, partial, data, n_rows, row_len, ld, init, inplace, main_op, reduce_op, final_op, seg_vecs);

@@ -4,10 +4,12 @@
 //
 // Read-reduce-rescale in ONE pass over HBM: 2 x sizeof(T) bytes per element.
 //
-//  row_normalize_kernel       rows of up to 256 16-byte vectors (1024 fp32): a sub-warp of G lanes
+//  row_normalize_kernel       rows of up to 512 16-byte vectors (2048 fp32): a sub-warp of G lanes
 //                             holds the whole row in registers (CPL vectors per lane), U rows at a
-//                             time so that 8 loads are in flight per lane; butterfly reduction, then
-//                             the same registers are divided and stored.
+//                             time so that 8 or 16 loads are in flight per lane; butterfly reduction,
+//                             then the same registers are divided and stored.
+//  row_normalize_cta_kernel   rows of up to 4096 vectors (16384 fp32): one CTA per row, 4 / 8 / 16
+//                             vectors per thread in registers, one barrier per row.
 //  row_normalize_long_kernel  longer rows: one CTA per row, two sweeps; the second sweep re-reads the
 //                             row from L1 / L2 (it was just touched), so DRAM still sees it once.
 #pragma once
@@ -99,6 +101,74 @@ __global__ void __launch_bounds__(256) row_normalize_kernel(T* out,
   }
 }
 
+// One CTA per row, the row held in registers (CPT vectors per thread): rows of up to 256 * CPT vectors.
+template <typename T, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp, int VEC, int CPT>
+__global__ void __launch_bounds__(256) row_normalize_cta_kernel(T* out,
+                                                               const T* in,
+                                                               int64_t n_rows,
+                                                               int64_t n_cols,
+                                                               T init,
+                                                               T eps,
+                                                               MainOp main_op,
+                                                               ReduceOp reduce_op,
+                                                               FinalOp final_op)
+{
+  using State = typename state_for<T, ReduceOp>::type;
+  __shared__ State s_state[2][8];  // double-buffered: one barrier per row
+  const int tid  = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nvec = int(n_cols / VEC);
+  bool chunk_ok[CPT];
+#pragma unroll
+  for (int k = 0; k < CPT; ++k)
+    chunk_ok[k] = k * 256 + tid < nvec;
+  int phase = 0;
+  for (int64_t r = blockIdx.x; r < n_rows; r += gridDim.x, phase ^= 1) {
+    const T* src = in + r * n_cols;
+    VecOf<T, VEC> v[CPT];
+#pragma unroll
+    for (int k = 0; k < CPT; ++k)
+      v[k] = load_stream<T, VEC>(src + int64_t(chunk_ok[k] ? k * 256 + tid : 0) * VEC);
+    State st;
+    st.init(init);
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) {
+      if (chunk_ok[k]) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          st.push(T(main_op(v[k].e[e], IdxT((k * 256 + tid) * VEC + e))), reduce_op);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      State got = shfl_xor_any(st, off);
+      st.merge(got, reduce_op);
+    }
+    if (lane == 0) s_state[phase][warp] = st;
+    __syncthreads();
+    // every thread folds the eight warp results in the same order: the same norm everywhere
+    State tot = s_state[phase][0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w)
+      tot.merge(s_state[phase][w], reduce_op);
+    const T norm = T(final_op(tot.value()));
+    if (!(norm <= eps)) {
+      T* dst = out + r * n_cols;
+#pragma unroll
+      for (int k = 0; k < CPT; ++k) {
+        if (chunk_ok[k]) {
+          VecOf<T, VEC> o;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            o.e[e] = v[k].e[e] / norm;
+          store_vec<T, VEC>(dst + int64_t(k * 256 + tid) * VEC, o);
+        }
+      }
+    }
+  }
+}
+
 template <typename T, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp, int VEC>
 __global__ void __launch_bounds__(256) row_normalize_long_kernel(T* out,
                                                                 const T* in,
@@ -168,9 +238,6 @@ __global__ void __launch_bounds__(256) row_normalize_long_kernel(T* out,
   }
 }
 
-// Rows of up to kNormRegVecs vectors stay in registers.
-constexpr int kNormRegVecs = 256;
-
 template <typename T, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp>
 cudaError_t launch_row_normalize(T* out,
                                  const T* in,
@@ -192,7 +259,7 @@ cudaError_t launch_row_normalize(T* out,
 
 #define B2R_NORMALIZE_REG(VEC_, CPL_)                                                                     \
   do {                                                                                                    \
-    constexpr int U_ = 8 / CPL_;                                                                          \
+    constexpr int U_ = CPL_ >= 8 ? 1 : 8 / CPL_;                                                         \
     auto kern        = row_normalize_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_, CPL_, U_>;          \
     static int occ   = resident_ctas(kern, 256, 0);                                                       \
     const unsigned g = next_pow2(unsigned(ceil_div<int64_t>(nvec, CPL_)));                                \
@@ -204,15 +271,32 @@ cudaError_t launch_row_normalize(T* out,
     kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,      \
                                              final_op, G);                                                \
   } while (0)
+#define B2R_NORMALIZE_CTA(VEC_, CPT_)                                                                     \
+  do {                                                                                                    \
+    auto kern      = row_normalize_cta_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_, CPT_>;            \
+    static int occ = resident_ctas(kern, 256, 0);                                                         \
+    int64_t ctas   = n_rows;                                                                              \
+    if (ctas > int64_t(sms) * occ * 2) ctas = int64_t(sms) * occ * 2;                                     \
+    kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,      \
+                                             final_op);                                                   \
+  } while (0)
 #define B2R_NORMALIZE_ANY(VEC_)                                                                           \
   do {                                                                                                    \
-    if (nvec > kNormRegVecs) {                                                                            \
+    if (nvec > 4096) {                                                                                    \
       auto kern      = row_normalize_long_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_>;               \
       static int occ = resident_ctas(kern, 256, 0);                                                       \
       int64_t ctas   = n_rows;                                                                            \
       if (ctas > int64_t(sms) * occ) ctas = int64_t(sms) * occ;                                           \
       kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,    \
                                                final_op);                                                 \
+    } else if (nvec > 2048) {                                                                             \
+      B2R_NORMALIZE_CTA(VEC_, 16);                                                                        \
+    } else if (nvec > 1024) {                                                                             \
+      B2R_NORMALIZE_CTA(VEC_, 8);                                                                         \
+    } else if (nvec > 512) {                                                                              \
+      B2R_NORMALIZE_CTA(VEC_, 4);                                                                         \
+    } else if (nvec > 256) {                                                                              \
+      B2R_NORMALIZE_REG(VEC_, 16);                                                                        \
     } else if (nvec > 128) {                                                                              \
       B2R_NORMALIZE_REG(VEC_, 8);                                                                         \
     } else if (nvec >= 32) {                                                                              \
@@ -229,6 +313,7 @@ cudaError_t launch_row_normalize(T* out,
     B2R_NORMALIZE_ANY(1);
   }
 #undef B2R_NORMALIZE_ANY
+#undef B2R_NORMALIZE_CTA
 #undef B2R_NORMALIZE_REG
   return cudaGetLastError();
 }

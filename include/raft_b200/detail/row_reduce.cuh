@@ -305,6 +305,13 @@ __global__ void __launch_bounds__(TPB) row_split_kernel(StoreT* __restrict__ out
       for (int e = 0; e < VEC; ++e)
         st[0].push(OutT(main_op(v.e[e], IdxT(c * VEC + e))), reduce_op);
     }
+    if constexpr (VEC > 1) {
+      // a row length that is no multiple of the vector width: the last segment takes the tail
+      if (seg == n_seg - 1) {
+        for (int64_t i = nvec * VEC + threadIdx.x; i < row_len; i += TPB)
+          st[0].push(OutT(main_op(rp[i], IdxT(i))), reduce_op);
+      }
+    }
 #pragma unroll
     for (int u = 1; u < U; ++u)
       st[0].merge(st[u], reduce_op);

@@ -29,7 +29,7 @@ FLAGS=(-std=c++20 --expt-extended-lambda --expt-relaxed-constexpr -gencode arch=
        -I"$HERE/ref_shim" -I"$CCCL/libcudacxx/include" -I"$CCCL/cub" -I"$CCCL/thrust"
        -I"$REF/cpp/include" -I"$HERE/../include")
 pids=()
-TUS=(ref_reduce_rows ref_reduce_cols ref_bykey_kvp ref_normalize)
+TUS=(ref_reduce_rows ref_reduce_cols ref_bykey_kvp ref_normalize ref_map_reduce)
 for tu in "${TUS[@]}"; do
   if [ "$OUT/$tu.o" -nt "$HERE/$tu.cu" ] && [ "$OUT/$tu.o" -nt "$HERE/ref_common.cuh" ]; then continue; fi
   nvcc "${FLAGS[@]}" -c "$HERE/$tu.cu" -o "$OUT/$tu.o" &

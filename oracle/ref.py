@@ -27,6 +27,8 @@ def load():
             getattr(lib, name).argtypes = [ctypes.POINTER(L.ReduceDesc), vp, vp, vp]
         lib.ref_rows_by_key.argtypes = [vp, vp, i64, vp, vp, i32, i64, i64, i64, i32, vp]
         lib.ref_cols_by_key.argtypes = [vp, vp, vp, i32, i64, i64, i64, i32, vp]
+        lib.ref_map_then_sum_reduce.argtypes = [vp, vp, i32, i64, vp]
+        lib.ref_map_reduce_minmax.argtypes = [vp, vp, i64, i32, ctypes.c_float, vp]
         lib.ref_row_normalize.argtypes = [vp, vp, i32, i64, i64, i32, vp]
         _lib = lib
     return _lib
@@ -80,3 +82,19 @@ def row_normalize(out, data, norm_type):
     with torch.cuda.device(data.device):
         return load().ref_row_normalize(out.data_ptr(), data.data_ptr(), _DTYPES[data.dtype], n_rows, n_cols,
                                         _NORM[norm_type], _stream(data.device))
+
+
+def map_then_sum_reduce(out, data):
+    """The reference's mapThenSumReduce(out, len, identity_op, stream, data)."""
+    from raft_b200.linalg import _DTYPES
+    with torch.cuda.device(data.device):
+        return load().ref_map_then_sum_reduce(out.data_ptr(), data.data_ptr(), _DTYPES[data.dtype], data.numel(),
+                                              _stream(data.device))
+
+
+def map_reduce_minmax(out, data, reduce_op, neutral):
+    """The reference's map_reduce with identity_op and cuda::minimum ("min") / cuda::maximum ("max"), float."""
+    with torch.cuda.device(data.device):
+        return load().ref_map_reduce_minmax(out.data_ptr(), data.data_ptr(), data.numel(),
+                                            L.REDUCE_MIN if reduce_op == "min" else L.REDUCE_MAX, float(neutral),
+                                            _stream(data.device))

@@ -320,6 +320,20 @@ def argmax(data, out=None, index_dtype=torch.int32):
     return _matrix_arg("b2r_matrix_argmax", data, out, index_dtype)
 
 
+def map_reduce(data, map_op="identity", reduce_op="add", neutral=0.0, out=None, out_dtype=None, workspace=None):
+    """raft::linalg::mapReduce / mapThenSumReduce for the named map functors
+    (linalg/map_reduce.cuh:43-103, linalg/map_then_reduce.cuh:37-53):
+    out[0] = reduce_op over i of map_op(data[i]); `neutral` is the identity of reduce_op.
+    `data` is any contiguous tensor, read as a flat array. Returns a one-element tensor."""
+    _require_cuda(data, "data")
+    if not data.is_contiguous():
+        raise ValueError("Input must be contiguous")
+    flat = data.reshape(1, -1)
+    if out is None:
+        out = torch.empty(1, dtype=out_dtype or data.dtype, device=data.device)
+    return reduce(flat, ALONG_ROWS, out, init=neutral, main_op=map_op, reduce_op=reduce_op, workspace=workspace)
+
+
 def row_normalize(data, norm_type="L2", out=None, eps=1e-8):
     """raft::linalg::row_normalize<norm_type> (linalg/normalize.cuh:88-107): every row of a
     row-major matrix divided by its L1 / L2 / Linf norm. A row whose norm is <= eps is not

@@ -7,10 +7,18 @@
 //   - device lambdas as main / final op (the way stats::stddev and weighted_mean call reduce)
 //   - reduce_rows_by_key incl. the (ncols, nrows) mdspan convention (reduce_rows_by_key.cu:134-147)
 //   - reduce_cols_by_key incl. nkeys inferred from the output view
+//   - row_normalize: the three norm types, a user functor triple, rows below eps left untouched
+//     (cpp/tests/linalg/normalize.cu:38-98)
+//   - mapThenSumReduce / map_reduce: sum against a host loop, a two-array map (squared difference,
+//     as linalg/detail/mean_squared_error.cuh calls it), and the min = 1 / max = 5 known answers of
+//     cpp/tests/linalg/map_then_reduce.cu:133-171
 //   - shape errors -> raft::logic_error, unsupported strided output type -> raft::exception
 // Prints one line per check and "ALL PASSED" / exits non-zero.
 #include <raft/linalg/coalesced_reduction.cuh>
+#include <raft/linalg/map_reduce.cuh>
+#include <raft/linalg/map_then_reduce.cuh>
 #include <raft/linalg/norm.cuh>
+#include <raft/linalg/normalize.cuh>
 #include <raft/linalg/reduce.cuh>
 #include <raft/linalg/reduce_cols_by_key.cuh>
 #include <raft/linalg/reduce_rows_by_key.cuh>
@@ -19,6 +27,7 @@
 #include <raft/matrix/argmin.cuh>
 
 #include <cmath>
+#include <limits>
 #include <cstdio>
 #include <cstdlib>
 #include <random>
@@ -401,6 +410,120 @@ static void test_matrix_arg()
   CHECK(ok, "matrix::argmin 5000x200 with ties (lowest index)");
 }
 
+// L3 norm through user functors: |x|^3 summed, cube root at the end
+struct CubeAbs {
+  __host__ __device__ float operator()(float x, int) const { return fabsf(x) * x * x; }
+};
+struct CubeRoot {
+  __host__ __device__ float operator()(float x) const { return cbrtf(x); }
+};
+
+static void test_row_normalize(int rows, int cols)
+{
+  raft::resources handle;
+  auto h = random_matrix(rows, cols, 21);
+  for (int c = 0; c < cols; ++c)
+    h[size_t(rows / 2) * cols + c] = 0.f;  // a zero row: must not be written
+  DevBuf<float> d(h);
+  auto in = raft::make_device_matrix_view<const float, int, raft::row_major>(d.p, rows, cols);
+  char name[96];
+  for (int t = 0; t < 4; ++t) {
+    std::vector<float> sentinel(size_t(rows) * cols, 7.f);
+    DevBuf<float> o(sentinel);
+    auto out = raft::make_device_matrix_view<float, int, raft::row_major>(o.p, rows, cols);
+    if (t == 0) raft::linalg::row_normalize<raft::linalg::L1Norm>(handle, in, out);
+    if (t == 1) raft::linalg::row_normalize<raft::linalg::L2Norm>(handle, in, out);
+    if (t == 2) raft::linalg::row_normalize<raft::linalg::LinfNorm>(handle, in, out);
+    if (t == 3) raft::linalg::row_normalize(handle, in, out, 0.f, CubeAbs{}, raft::add_op{}, CubeRoot{});
+    std::vector<double> e(size_t(rows) * cols);
+    for (int r = 0; r < rows; ++r) {
+      double acc = 0;
+      for (int c = 0; c < cols; ++c) {
+        const double x = std::fabs(double(h[size_t(r) * cols + c]));
+        acc            = t == 0 ? acc + x : t == 1 ? acc + x * x : t == 2 ? std::fmax(acc, x) : acc + x * x * x;
+      }
+      const double nrm = t == 1 ? std::sqrt(acc) : t == 3 ? std::cbrt(acc) : acc;
+      for (int c = 0; c < cols; ++c)
+        e[size_t(r) * cols + c] = nrm <= 1e-8 ? 7.0 : double(h[size_t(r) * cols + c]) / nrm;
+    }
+    static const char* what[] = {"L1", "L2", "Linf", "user functors (L3)"};
+    std::snprintf(name, sizeof(name), "row_normalize %s %dx%d", what[t], rows, cols);
+    CHECK(all_approx(e, o.host(), 1e-5), name);
+  }
+  bool threw = false;
+  try {
+    DevBuf<float> o(size_t(rows) * cols);
+    raft::linalg::row_normalize<raft::linalg::L2Norm>(
+      handle, in, raft::make_device_matrix_view<float, int, raft::row_major>(o.p, rows, cols - 1));
+  } catch (const raft::logic_error&) {
+    threw = true;
+  }
+  CHECK(threw, "  ... column mismatch throws logic_error");
+}
+
+struct SqDiff {
+  __host__ __device__ float operator()(float a, float b) const { return (a - b) * (a - b); }
+};
+struct MinOf {
+  template <typename T>
+  __host__ __device__ T operator()(T a, T b) const { return a < b ? a : b; }
+};
+struct MaxOf {
+  template <typename T>
+  __host__ __device__ T operator()(T a, T b) const { return a > b ? a : b; }
+};
+
+static void test_map_reduce()
+{
+  raft::resources handle;
+  cudaStream_t stream = raft::resource::get_cuda_stream(handle);
+  char name[96];
+  for (size_t len : {size_t(1), size_t(1237), size_t(1024 * 1024), size_t(1024 * 1024 + 1), size_t(3 * 1000 * 1000 + 2)}) {
+    std::mt19937 gen(1234);
+    std::uniform_real_distribution<float> dist(-1.f, 1.f);
+    std::vector<float> a(len), b(len);
+    double sum = 0, sq = 0;
+    for (size_t i = 0; i < len; ++i) {
+      a[i] = dist(gen);
+      b[i] = dist(gen);
+      sum += a[i];
+      sq += double((a[i] - b[i]) * (a[i] - b[i]));
+    }
+    DevBuf<float> da(a), db(b), of(1);
+    DevBuf<double> od(1);
+    raft::linalg::mapThenSumReduce(of.p, len, raft::identity_op{}, stream, da.p);
+    std::snprintf(name, sizeof(name), "mapThenSumReduce identity float len %zu", len);
+    CHECK(approx(sum, of.host()[0], 1e-3), name);
+    raft::linalg::mapThenSumReduce(od.p, len, raft::identity_op{}, stream, da.p);
+    CHECK(approx(sum, od.host()[0], 1e-6 * std::sqrt(double(len))), "  ... float -> double");
+    raft::linalg::mapThenSumReduce<float, SqDiff, size_t, 256, const float*>(of.p, len, SqDiff{}, stream, da.p,
+                                                                              (const float*)db.p);
+    CHECK(approx(sq, of.host()[0], 1e-5), "  ... two arrays (squared difference)");
+  }
+  {  // known answers: values in [2, 3), one 1 and one 5 planted (map_then_reduce.cu:133-171)
+    const int n = 1237;
+    std::mt19937 gen(137);
+    std::uniform_real_distribution<float> dist(2.f, 3.f);
+    std::vector<float> h(n);
+    for (auto& x : h)
+      x = dist(gen);
+    h[42]  = 1.f;
+    h[337] = 5.f;
+    DevBuf<float> d(h), o(1);
+    DevBuf<double> o2(1);
+    auto in = raft::make_device_vector_view<const float>(d.p, static_cast<std::uint32_t>(n));
+    raft::linalg::map_reduce(handle, in, raft::make_device_scalar_view(o.p), std::numeric_limits<float>::max(),
+                             raft::identity_op{}, MinOf{});
+    CHECK(o.host()[0] == 1.f, "map_reduce min known answer 1");
+    raft::linalg::map_reduce(handle, in, raft::make_device_scalar_view(o.p), std::numeric_limits<float>::min(),
+                             raft::identity_op{}, MaxOf{});
+    CHECK(o.host()[0] == 5.f, "map_reduce max known answer 5");
+    raft::linalg::map_reduce(handle, in, raft::make_device_scalar_view(o2.p), double(std::numeric_limits<float>::min()),
+                             raft::identity_op{}, raft::max_op{});
+    CHECK(o2.host()[0] == 5.0, "  ... float -> double with raft::max_op (library path)");
+  }
+}
+
 static void test_errors()
 {
   raft::resources handle;
@@ -462,6 +585,9 @@ int main()
   test_cols_by_key(9, 9999, 42);
   test_cols_by_key(1024, 1234, 127);
   test_matrix_arg();
+  for (int cols : {3, 33, 128, 500, 1500, 5000, 20000})
+    test_row_normalize(257, cols);
+  test_map_reduce();
   test_errors();
   cudaDeviceSynchronize();
   const cudaError_t e = cudaGetLastError();

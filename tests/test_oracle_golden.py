@@ -137,3 +137,25 @@ def test_synth_golden(oracle):
     assert np.array_equal(g["int_f32"], oracle.synth((64,), np.float32, 3, "int", 0, 16))
     assert np.array_equal(g["keys_i32"], oracle.synth((64,), np.int32, 5, "int", 0, 1024))
     assert np.array_equal(g["uniform_f64"], oracle.synth((64,), np.float64, 2, "uniform", 0, 1))
+
+
+def test_map_reduce_known_answers(oracle):
+    # cpp/tests/linalg/map_then_reduce.cu:133-171: 1237 values in [2, 3), a 1 planted at index 42 and a
+    # 5 at 337; min with neutral numeric_limits::max gives 1, max with neutral numeric_limits::min gives 5
+    v = oracle.synth((1237,), np.float32, 137, "uniform", 2, 3)
+    v[42], v[337] = 1.0, 5.0
+    lo = oracle.reduce(v.reshape(1, -1), reduce_op="min", init=float(np.finfo(np.float32).max))
+    hi = oracle.reduce(v.reshape(1, -1), reduce_op="max", init=float(np.finfo(np.float32).tiny))
+    assert lo[0] == 1.0 and hi[0] == 5.0
+
+
+def test_row_normalize_known_answers(oracle):
+    # hand-checkable rows: (3, 4) has L1 7, L2 5, Linf 4; a zero row keeps the previous content
+    x = np.array([[3, 4], [0, 0], [-6, 8]], dtype=np.float32)
+    prev = np.full_like(x, 9)
+    assert np.array_equal(oracle.row_normalize(x, "L2", prev=prev),
+                          np.array([[0.6, 0.8], [9, 9], [-0.6, 0.8]], dtype=np.float32))
+    assert np.array_equal(oracle.row_normalize(x, "Linf", prev=prev),
+                          np.array([[0.75, 1], [9, 9], [-0.75, 1]], dtype=np.float32))
+    assert np.allclose(oracle.row_normalize(x.astype(np.float64), "L1", prev=prev.astype(np.float64)),
+                       np.array([[3 / 7, 4 / 7], [9, 9], [-6 / 14, 8 / 14]]), rtol=0, atol=1e-15)
