@@ -45,6 +45,9 @@ WORKLOADS = {
     "c3mean": (16_777_216, 64, "column mean (strided_reduction, div_const n_rows) fp32 16777216x64 U[0,1) seed 2"),
     "c4": (8_388_608, 64, "row argmin KeyValuePair<int,float> fp32 8388608x64 U{0..15} seed 3"),
     "c5": (10_000_000, 128, "reduce_rows_by_key fp32 10000000x128 N(0,1) seed 4, int32 keys U[0,1024) seed 5"),
+    # the callers next to the path (not baseline configs; never the default workload)
+    "normalize": (100_000, 1024, "row_normalize L2 fp32 100000x1024 U[-10,10) seed 6 (read + write)"),
+    "mapsum": (1_048_576, 1024, "mapThenSumReduce identity fp32, 2^30 elements U[-1,1) seed 7"),
 }
 NKEYS = 1024
 
@@ -60,11 +63,15 @@ def algorithmic_bytes(name):
         return inp + rows * 8
     if name == "c5":
         return inp + rows * 4 + NKEYS * cols * 4 + NKEYS * 8
+    if name == "normalize":
+        return 2 * inp
+    if name == "mapsum":
+        return inp + 4
     raise KeyError(name)
 
 
 def launches_per_step(name):
-    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 6}[name]
+    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 6, "normalize": 1, "mapsum": 2}[name]
 
 
 class Workload:
@@ -92,6 +99,10 @@ class Workload:
             linalg.synth_fill(self.data, 4, "normal", first_index=base)
             self.keys = torch.empty((rows,), dtype=torch.int32, device=device)
             linalg.synth_fill(self.keys, 5, "int", 0, NKEYS, first_index=first_row)
+        elif name == "normalize":
+            linalg.synth_fill(self.data, 6, "uniform", -10, 10, first_index=base)
+        elif name == "mapsum":
+            linalg.synth_fill(self.data, 7, "uniform", -1, 1, first_index=base)
         if name in ("c1", "c2", "c2sq"):
             self.out = torch.empty(rows, dtype=torch.float32, device=device)
         elif name in ("c3", "c3mean"):
@@ -101,6 +112,10 @@ class Workload:
         elif name == "c5":
             self.out = torch.empty((NKEYS, cols), dtype=torch.float32, device=device)
             self.counts = torch.empty(NKEYS, dtype=torch.int64, device=device)
+        elif name == "normalize":
+            self.out = torch.zeros_like(self.data)
+        elif name == "mapsum":
+            self.out = torch.zeros(1, dtype=torch.float32, device=device)
         # scratch allocated once, outside the timed region (a caller-provided workspace)
         self.ws = None
         if impl == "ours":
@@ -109,6 +124,8 @@ class Workload:
                 need = linalg.reduce_workspace_bytes(self.data, linalg.ALONG_COLUMNS)
             elif name == "c5":
                 need = linalg.reduce_rows_by_key_workspace_bytes(self.data, NKEYS)
+            elif name == "mapsum":
+                need = linalg.reduce_workspace_bytes(self.data.reshape(1, -1))
             if need:
                 self.ws = torch.empty(need, dtype=torch.uint8, device=device)
         else:
@@ -148,6 +165,13 @@ class Workload:
                     import torch.distributed as dist
                     dist.all_reduce(self.out)     # 1024 x 128 fp32 partial tables
                     dist.all_reduce(self.counts)  # 1024 int64 counts
+            elif n == "normalize":
+                la.row_normalize(data, "L2", out=self.out)
+            elif n == "mapsum":
+                la.map_reduce(data, out=self.out, workspace=self.ws)
+                if self.world > 1:
+                    import torch.distributed as dist
+                    dist.all_reduce(self.out)
         else:
             r = self.ref
             st = 0
@@ -167,6 +191,10 @@ class Workload:
                               init=float("inf"))
             elif n == "c5":
                 st = r.rows_by_key(self.out, data, self.keys if keys is None else keys, NKEYS)
+            elif n == "normalize":
+                st = r.row_normalize(self.out, data, "L2")
+            elif n == "mapsum":
+                st = r.map_then_sum_reduce(self.out, data)
             if st != 0:
                 raise RuntimeError(f"reference wrapper status {st} for {n}")
 
@@ -271,10 +299,12 @@ def cpu_baseline(name, budget_rows=None):
     from oracle import oracle as o
     rows, cols, _ = WORKLOADS[name]
     sample_rows = min(rows, budget_rows or {"c1": 4096, "c2": 1_000_000, "c2sq": 1_000_000, "c3": 2_000_000,
-                                            "c3mean": 2_000_000, "c4": 2_000_000, "c5": 1_000_000}[name])
+                                            "c3mean": 2_000_000, "c4": 2_000_000, "c5": 1_000_000,
+                                            "normalize": 100_000, "mapsum": 262_144}[name])
     seed, kind, lo, hi = {"c1": (0, "uniform", -1, 1), "c2": (1, "normal", 0, 1), "c2sq": (1, "normal", 0, 1),
                           "c3": (2, "uniform", 0, 1), "c3mean": (2, "uniform", 0, 1), "c4": (3, "int", 0, 16),
-                          "c5": (4, "normal", 0, 1)}[name]
+                          "c5": (4, "normal", 0, 1), "normalize": (6, "uniform", -10, 10),
+                          "mapsum": (7, "uniform", -1, 1)}[name]
     data = o.synth((sample_rows, cols), np.float32, seed, kind, lo, hi)
     keys = o.synth((sample_rows,), np.int32, 5, "int", 0, NKEYS) if name == "c5" else None
 
@@ -291,6 +321,10 @@ def cpu_baseline(name, budget_rows=None):
             o.omp_row_argmin(data)
         elif name == "c5":
             o.omp_rows_by_key(data, keys, NKEYS)
+        elif name == "normalize":
+            o.row_normalize(data, "L2")
+        elif name == "mapsum":
+            float(o.omp_row_sum(data).astype(np.float64).sum())  # rows in parallel, then the row sums
 
     once()
     reps, t0 = 0, time.perf_counter()
@@ -503,7 +537,7 @@ def main():
     line = {"metric": "hbm_gb_per_s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4") or world == 1
+            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4", "normalize") or world == 1
                                                         else "per-GPU partials + NCCL all-reduce inside the step"),
                        "l2": "L2 flushed by a 378 MB write before every step" if flush
                        else f"input {rows * cols * 4 >> 20} MB per GPU > 126 MB L2"},
@@ -524,7 +558,7 @@ def main():
         table = {}
         del w
         torch.cuda.empty_cache()
-        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5"):
+        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5", "normalize", "mapsum"):
             r, c, _ = WORKLOADS[cn]
             ent = {}
             for impl in ("ours", "reference"):
