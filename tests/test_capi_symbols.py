@@ -9,8 +9,8 @@ from raft_b200 import _lib
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared():
-    text = open(os.path.join(ROOT, "include", "raft_b200.h")).read()
+def _declared(header="raft_b200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"B2R_API\s+[\w\s\*]+?\b(b2r_\w+)\s*\(", text)))
 
@@ -42,3 +42,18 @@ def test_descriptor_layout_matches_the_header():
     assert ctypes.sizeof(_lib.ReduceDesc) == 80
     assert _lib.ReduceDesc.n_rows.offset == 16 and _lib.ReduceDesc.init.offset == 48
     assert _lib.ReduceDesc.final_scalar.offset == 72
+
+
+def test_multi_device_library_exports_every_declared_symbol():
+    """libraft_b200_mg.so (NCCL layer, include/raft_b200_mg.h). Loading needs NCCL on the loader path;
+    no device call is made."""
+    path = os.path.join(ROOT, "raft_b200", "libraft_b200_mg.so")
+    assert os.path.exists(path), "run __graft_entry__.build() first"
+    ctypes.CDLL(_lib.LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+    lib = ctypes.CDLL(path)
+    names = _declared("raft_b200_mg.h")
+    assert "b2r_mg_reduce" in names and "b2r_mg_reduce_rows_by_key" in names and "b2r_mg_comm_create" in names
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in raft_b200_mg.h but not exported"
+    lib.b2r_mg_comm_size.argtypes = [ctypes.c_void_p]
+    assert lib.b2r_mg_comm_size(None) == 0

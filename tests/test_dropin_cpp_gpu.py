@@ -36,3 +36,14 @@ def test_reference_stats_on_overlay(cuda):
     if not os.path.exists(binary):
         pytest.skip("overlay build needs the reference checkout at build time")
     _run(binary)
+
+
+def test_multi_device_layer(cuda):
+    """include/raft_b200_mg.h (one host process, NCCL) on every visible device: tests/cpp/test_mg.cu.
+    One device exercises the whole call path with a one-rank communicator; two or more add the
+    all-reduce across devices and unequal / empty shards."""
+    binary = os.path.join(HERE, "cpp", "test_mg")
+    assert os.path.exists(binary), "build it with `make -C tests/cpp` (done by __graft_entry__.build())"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([binary], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "ALL PASSED" in r.stdout, r.stdout[-4000:]
