@@ -34,9 +34,9 @@ typedef struct b2r_mg_comm b2r_mg_comm;
  * NCCL communicators (ncclCommInitAll) and one non-blocking stream per device. */
 B2R_API int b2r_mg_comm_create(b2r_mg_comm** comm, const int* devices, int n_devices);
 
-/* Same, on NCCL communicators the caller owns (`nccl_comms[d]` is the ncclComm_t of devices[d], as
- * raft::resource::get_nccl_comm gives per rank of a device_resources_snmg); they are not destroyed
- * by b2r_mg_comm_destroy. */
+/* Same, on NCCL communicators the caller owns (`nccl_comms[d]` is the ncclComm_t of devices[d], e.g.
+ * raft::resource::get_nccl_comms(handle)[d] of a device_resources_snmg, core/resource/nccl_comm.hpp:70-95);
+ * they are not destroyed by b2r_mg_comm_destroy. */
 B2R_API int b2r_mg_comm_adopt(b2r_mg_comm** comm, const int* devices, int n_devices, void* const* nccl_comms);
 
 B2R_API int b2r_mg_comm_destroy(b2r_mg_comm* comm);
