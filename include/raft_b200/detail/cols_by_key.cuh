@@ -1,17 +1,20 @@
 // Keyed column sums:  out[r][keys[c]] += data[r][c]   for a row-major [nrows x ncols] matrix.
 //
 // Counterpart of the reference's cached / direct kernels
-// (linalg/detail/reduce_cols_by_key.cuh:23-68, dispatch :89-138). A CTA owns a tile of
-// RT rows and a contiguous range of columns, accumulates into a privatised
-// [RT x nkeys] table in shared memory (shared-memory atomics; lanes of a warp read 128
-// contiguous bytes of one row per step) and flushes the table once. When one CTA covers
-// whole rows the flush is a plain store (no memset, no global atomics); when the columns
-// of a row are split across CTAs the flush uses global atomics on a zeroed output.
-// Tables too large for shared memory fall back to global atomics per element.
+// (linalg/detail/reduce_cols_by_key.cuh:23-68, dispatch :89-138). Two algorithms:
+//  * sorted column tiles (cols_by_key_sorted.cuh) for large inputs with up to a few hundred keys:
+//    no floating-point atomics, TMA-staged tiles;
+//  * the kernels of this file otherwise: a CTA owns a tile of RT rows and a contiguous range of
+//    columns, accumulates into a privatised [RT x nkeys] table in shared memory (shared-memory
+//    atomics; lanes of a warp read 128 contiguous bytes of one row per step) and flushes the
+//    table once. When one CTA covers whole rows the flush is a plain store (no memset, no global
+//    atomics); when the columns of a row are split across CTAs the flush uses global atomics on a
+//    zeroed output. Tables too large for shared memory fall back to global atomics per element.
 #pragma once
 
 #include "common.cuh"
 #include "launch.cuh"
+#include "cols_by_key_sorted.cuh"
 
 namespace raft_b200 {
 namespace detail {
@@ -102,6 +105,11 @@ cudaError_t launch_cols_by_key(T* out,
   cudaError_t e;
   const size_t out_bytes = size_t(nrows) * nkeys * sizeof(T);
   if (ncols <= 0) return reset ? cudaMemsetAsync(out, 0, out_bytes, stream) : cudaSuccess;
+  // sorted column tiles where they win (large inputs, a few hundred keys at most)
+  const int algo = tuning().colkey_algo;
+  if (algo != 1 && cols_by_key_sorted_supported<T>(nrows, ncols, nkeys) &&
+      (algo == 2 || cols_by_key_sorted_preferred<T>(nrows, ncols, nkeys)))
+    return launch_cols_by_key_sorted<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream);
 
   const size_t budget  = size_t(96) << 10;  // two CTAs per SM keep loads in flight across the flush
   const size_t per_row = size_t(nkeys) * sizeof(T);

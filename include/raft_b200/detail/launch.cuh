@@ -112,6 +112,8 @@ struct Tuning {
   int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
   int key_algo             = 0;     // B2R_KEY_ALGO   0: auto, 1: shared-memory table, 2: sort then stream
+  int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted column tiles
+  int colkey_tma           = 1;     // B2R_COLKEY_TMA 1: TMA-staged ring for the sorted column tiles, 2: off
   int col_tma              = 1;     // B2R_COL_TMA    1: TMA-staged tiles for narrow contiguous column reductions, 2: off
   int col_tma_tile_kb      = 32;    // B2R_COL_TMA_KB tile size of the TMA ring, KiB
   int tma_stages           = 4;     // B2R_TMA_STAGES stages of the TMA ring (2..8)
@@ -140,6 +142,8 @@ inline Tuning tuning()
   x.key_block_rows       = env_int("B2R_KEY_BLOCK", x.key_block_rows);
   x.key_window_rows      = env_int("B2R_KEY_WINDOW", x.key_window_rows);
   x.key_algo             = env_int("B2R_KEY_ALGO", x.key_algo);
+  x.colkey_algo          = env_int("B2R_COLKEY_ALGO", x.colkey_algo);
+  x.colkey_tma           = env_int("B2R_COLKEY_TMA", x.colkey_tma);
   x.col_tma              = env_int("B2R_COL_TMA", x.col_tma);
   x.col_tma_tile_kb      = env_int("B2R_COL_TMA_KB", x.col_tma_tile_kb);
   x.tma_stages           = env_int("B2R_TMA_STAGES", x.tma_stages);

@@ -122,6 +122,51 @@ def test_cols_by_key_grid(cuda, oracle, rows, cols, nkeys, dt, tol):
     oracle.assert_approx(2 * exp, out.cpu().numpy(), 2 * tol, "accumulate")
 
 
+# the sorted-column-tiles kernels on every shape of the grid above (forced: the small ones would
+# take the single-kernel path), on shapes that exercise every tile geometry (RT 1..8, CH 256..4096,
+# columns split over CTAs or not, ragged last chunk and last row tile, scalar and 16-byte staging),
+# and the largest key count they take
+@pytest.mark.parametrize("rows,cols,nkeys", [(1, 1234, 7), (1, 101010, 2022), (9, 9999, 42), (63, 1234, 515),
+                                             (63, 101010, 127), (1024, 1234, 7), (1024, 9999, 2022),
+                                             (1024, 1234, 127), (9, 101010, 7), (2, 300, 8192), (5, 70000, 8192),
+                                             (4000, 4096, 64), (4001, 4100, 3), (300, 50001, 1), (20000, 256, 5),
+                                             (7, 8, 4), (100, 100000, 4096), (1000, 10000, 512)])
+@pytest.mark.parametrize("dt,tol", [(np.float32, 1e-5), (np.float64, 1e-9)])
+@pytest.mark.parametrize("key_dt", [np.int32, np.int64])
+@pytest.mark.parametrize("staging", ["tma", "registers"])
+def test_cols_by_key_sorted_tiles(cuda, oracle, monkeypatch, rows, cols, nkeys, dt, tol, key_dt, staging):
+    monkeypatch.setenv("B2R_COLKEY_ALGO", "2")
+    monkeypatch.setenv("B2R_COLKEY_TMA", "1" if staging == "tma" else "2")
+    data, hd = device_synth((rows, cols), dt, 1234, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((cols,), key_dt, 55, "int", 0, nkeys, cuda)
+    out = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys)
+    exp = oracle.cols_by_key(hd, hk, nkeys)
+    oracle.assert_approx(exp, out.cpu().numpy(), tol, "reset")
+    linalg.reduce_cols_by_key(data, keys, out=out, reset_sums=False)
+    oracle.assert_approx(2 * exp, out.cpu().numpy(), 2 * tol, "accumulate")
+    # no floating-point atomics: a repeat gives the same bits (fp64 segment sums of fp32 data)
+    if dt == np.float32:
+        again = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys)
+        assert torch.equal(again, linalg.reduce_cols_by_key(data, keys, nkeys=nkeys))
+
+
+def test_cols_by_key_single_kernel_path(cuda, oracle, monkeypatch):
+    monkeypatch.setenv("B2R_COLKEY_ALGO", "1")
+    data, hd = device_synth((2000, 3000), np.float32, 3, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((3000,), np.int32, 4, "int", 0, 77, cuda)
+    out = linalg.reduce_cols_by_key(data, keys, nkeys=77)
+    oracle.assert_approx(oracle.cols_by_key(hd, hk, 77), out.cpu().numpy(), 1e-3, "shared-memory atomics")
+
+
+def test_cols_by_key_unaligned_view(cuda, oracle):
+    """A matrix whose base pointer is only 4-byte aligned takes the scalar staging path."""
+    buf, _ = device_synth((1500 * 1000 + 1,), np.float32, 9, "uniform", -1, 1, cuda)
+    data = buf[1:].view(1500, 1000)
+    keys, hk = device_synth((1000,), np.int32, 4, "int", 0, 33, cuda)
+    out = linalg.reduce_cols_by_key(data, keys, nkeys=33)
+    oracle.assert_approx(oracle.cols_by_key(data.cpu().numpy(), hk, 33), out.cpu().numpy(), 1e-5, "unaligned")
+
+
 def test_cols_by_key_shape_errors(cuda):
     data = torch.ones((4, 6), device=cuda)
     keys = torch.zeros(6, dtype=torch.int32, device=cuda)
