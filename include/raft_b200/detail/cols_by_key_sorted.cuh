@@ -337,6 +337,7 @@ __global__ void __launch_bounds__(256) cbk_merge_kernel(T* __restrict__ out,
 constexpr int kCbkConsumers = 512;
 constexpr int kCbkTmaThreads = kCbkConsumers + 32;
 constexpr int kCbkMaxStages  = 4;
+constexpr int kCbkRegItems   = 4;  // (key, slice) items per warp slot whose sums stay in registers
 
 struct CbkStage {
   size_t off_tile, off_perm, off_offs, bytes;  // inside one stage
@@ -408,7 +409,10 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 1) cbk_tile_tma_kernel(T* __re
   const int lq      = 31 - __clz(Q);
   const int G       = lanes_per_row >> lq;
   const int slots   = (kCbkConsumers / 32) * G;  // (key, slice) items in flight per CTA step
-  const int S       = nkeys < slots ? slots / nkeys : 1;
+  int S = 1;  // a power of two: slices are cut with shifts
+  while (S * 2 * nkeys <= slots)
+    S <<= 1;
+  const int ls      = 31 - __clz(S);
   const int n_items = nkeys * S;
   const int n_work  = n_pairs * S;               // table cells, replicas included
 
@@ -467,6 +471,16 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 1) cbk_tile_tma_kernel(T* __re
     const int my_r = lane & (RT - 1);
     const int my_q = (lane >> lrt) & (Q - 1);
     const int my_g = lane >> (lrt + lq);
+    const int first_item = warp * G + my_g;
+    const int first_k    = S > 1 ? first_item % nkeys : first_item;
+    const int first_sl   = S > 1 ? first_item / nkeys : 0;
+    // up to kCbkRegItems items per warp slot (a few hundred keys at most): the lane's sums stay in
+    // registers for the whole row tile; more items go through the table in shared memory per tile
+    const bool in_regs = n_items <= kCbkRegItems * slots;
+    double run_sum[kCbkRegItems];
+#pragma unroll
+    for (int ii = 0; ii < kCbkRegItems; ++ii)
+      run_sum[ii] = 0.0;
     for (int i = tid; i < n_work; i += kCbkConsumers)
       acc[i] = 0.0;
     asm volatile("bar.sync 1, %0;" ::"n"(kCbkConsumers) : "memory");
@@ -488,42 +502,61 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 1) cbk_tile_tma_kernel(T* __re
         const uint32_t offs = st + uint32_t(lay.off_offs);   // u16 [nkeys + 1]
         const uint32_t row  = st + uint32_t(lay.off_tile) + uint32_t(my_r * stride) * uint32_t(sizeof(T));
         const uint32_t step = uint32_t(Q) * 2u;  // bytes between this lane's consecutive offsets
-        // every lane of the warp runs the same number of steps (shuffles inside)
-        for (int it0 = warp * G; it0 < n_items; it0 += slots) {
-          const int item  = it0 + my_g;
-          const bool live = item < n_items && my_r < rt;
-          double sum      = 0.0;
-          int cell        = 0;
-          if (live) {
-            const int k  = S > 1 ? item % nkeys : item;
-            const int sl = S > 1 ? item / nkeys : 0;
-            cell         = sl * n_pairs + (k << lrt) + my_r;
-            const unsigned seg0 = lds_u16(offs + 2u * unsigned(k)), len = lds_u16(offs + 2u * unsigned(k) + 2u) - seg0;
-            const unsigned j0 = seg0 + (S > 1 ? len * unsigned(sl) / unsigned(S) : 0u);
-            const unsigned j1 = seg0 + (S > 1 ? len * unsigned(sl + 1) / unsigned(S) : len);
-            double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
-            uint32_t pa       = perm + 2u * (j0 + unsigned(my_q));  // address of this lane's next offset
-            const uint32_t pe = perm + 2u * j1;
-            for (; pa + 3u * step < pe; pa += 4u * step) {
-              const unsigned a = lds_u16(pa), b = lds_u16(pa + step), c2 = lds_u16(pa + 2u * step),
-                             d = lds_u16(pa + 3u * step);
-              s0 += lds_as_double(row + a * unsigned(sizeof(T)), T());
-              s1 += lds_as_double(row + b * unsigned(sizeof(T)), T());
-              s2 += lds_as_double(row + c2 * unsigned(sizeof(T)), T());
-              s3 += lds_as_double(row + d * unsigned(sizeof(T)), T());
-            }
-            for (; pa < pe; pa += step)
-              s0 += lds_as_double(row + lds_u16(pa) * unsigned(sizeof(T)), T());
-            sum = (s0 + s1) + (s2 + s3);
+        // this lane's share of slice sl of the segment of key k in the staged tile
+        auto segment_sum = [&](int k, int sl) {
+          const unsigned seg0 = lds_u16(offs + 2u * unsigned(k)), len = lds_u16(offs + 2u * unsigned(k) + 2u) - seg0;
+          const unsigned j0 = seg0 + ((len * unsigned(sl)) >> ls);
+          const unsigned j1 = seg0 + ((len * unsigned(sl + 1)) >> ls);
+          double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+          uint32_t pa       = perm + 2u * (j0 + unsigned(my_q));  // address of this lane's next offset
+          const uint32_t pe = perm + 2u * j1;
+          for (; pa + 3u * step < pe; pa += 4u * step) {
+            const unsigned a = lds_u16(pa), b = lds_u16(pa + step), c2 = lds_u16(pa + 2u * step),
+                           d = lds_u16(pa + 3u * step);
+            s0 += lds_as_double(row + a * unsigned(sizeof(T)), T());
+            s1 += lds_as_double(row + b * unsigned(sizeof(T)), T());
+            s2 += lds_as_double(row + c2 * unsigned(sizeof(T)), T());
+            s3 += lds_as_double(row + d * unsigned(sizeof(T)), T());
           }
-          for (int off = RT; off < (RT << lq); off <<= 1)
-            sum += __shfl_xor_sync(0xffffffffu, sum, off);
-          if (live && my_q == 0) acc[cell] += sum;
+          for (; pa < pe; pa += step)
+            s0 += lds_as_double(row + lds_u16(pa) * unsigned(sizeof(T)), T());
+          return (s0 + s1) + (s2 + s3);
+        };
+        if (in_regs) {
+          if (my_r < rt) {
+#pragma unroll
+            for (int ii = 0; ii < kCbkRegItems; ++ii) {
+              const int item = first_item + ii * slots;  // item = slice * nkeys + key; slices only for ii == 0
+              if (item < n_items) run_sum[ii] += segment_sum(ii == 0 ? first_k : item, ii == 0 ? first_sl : 0);
+            }
+          }
+        } else {
+          // every lane of the warp runs the same number of steps (shuffles inside)
+          for (int it0 = warp * G; it0 < n_items; it0 += slots) {
+            const int item  = it0 + my_g;
+            const bool live = item < n_items && my_r < rt;
+            double sum      = live ? segment_sum(item, 0) : 0.0;  // more items than slots: S == 1
+            for (int off = RT; off < (RT << lq); off <<= 1)
+              sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (live && my_q == 0) acc[(item << lrt) + my_r] += sum;
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[s]);
       }
       // end of the row tile: flush the table ([k][r] -> out [r][k]) and clear it
+      if (in_regs) {
+#pragma unroll
+        for (int ii = 0; ii < kCbkRegItems; ++ii) {
+          double v = run_sum[ii];
+          for (int off = RT; off < (RT << lq); off <<= 1)
+            v += __shfl_xor_sync(0xffffffffu, v, off);
+          const int item = first_item + ii * slots;
+          if (item < n_items && my_r < rt && my_q == 0)
+            acc[(ii == 0 ? first_sl * n_pairs + (first_k << lrt) : (item << lrt)) + my_r] = v;
+          run_sum[ii] = 0.0;
+        }
+      }
       asm volatile("bar.sync 1, %0;" ::"n"(kCbkConsumers) : "memory");
       const bool failed = *abort_flag != 0;
       const double nan  = __longlong_as_double(0x7ff8000000000000ll);
@@ -560,7 +593,7 @@ inline bool cols_by_key_sorted_supported(int64_t nrows, int64_t ncols, int64_t n
 // a row tile spans several chunks (the table is flushed once per row tile), and keys few enough
 // that a (row, key) pair finds several columns of its key in a chunk - with one column or less
 // per pair the per-pair bookkeeping dominates and shared-memory atomics are faster. Measured on
-// 1000 x 100000 fp32: 8 keys 3.0 vs 0.6 TB/s, 128 keys 2.7 vs 1.2, 2048 keys 0.7 vs 1.3; on
+// 1000 x 100000 fp32: 8 keys 3.6 vs 0.6 TB/s, 128 keys 2.9 vs 1.2, 2048 keys 0.7 vs 1.3; on
 // 4096 x 4096 with 128 keys 1.4 vs 1.7.
 template <typename T>
 inline bool cols_by_key_sorted_preferred(int64_t nrows, int64_t ncols, int64_t nkeys)
