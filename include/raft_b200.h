@@ -313,6 +313,13 @@ B2R_API int b2r_synth_fill(void* dst,
  */
 B2R_API int b2r_trim_scratch_pool(void);
 
+/*
+ * Launch-shape knobs (environment variables B2R_*, listed in raft_b200/detail/launch.cuh) are read
+ * once, at the first call into the library. This call reads them again - for a benchmark that
+ * sweeps them within one process. It must not run concurrently with other calls.
+ */
+B2R_API int b2r_reload_tuning(void);
+
 B2R_API const char* b2r_status_string(int status);
 B2R_API int b2r_last_cuda_error(void);
 B2R_API const char* b2r_version(void);

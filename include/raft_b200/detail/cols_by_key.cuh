@@ -150,7 +150,7 @@ cudaError_t launch_cols_by_key(T* out,
   const size_t smem = size_t(RT) * per_row;
   auto kern         = cols_by_key_tile_kernel<T, KeyT>;
   if (smem > (size_t(48) << 10)) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    e = ensure_dynamic_smem(kern, size_t(smem));
     if (e != cudaSuccess) return e;
   }
   const dim3 grid{unsigned(tiles), unsigned(cx), 1u};

@@ -712,7 +712,7 @@ cudaError_t launch_cols_by_key_sorted(T* out,
   if (p.tma) {
     const CbkStage stage = cbk_stage<T>(p.RT, p.CH, p.offs_stride);
     auto kern            = cbk_tile_tma_kernel<T>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(p.smem));
+    e = ensure_dynamic_smem(kern, size_t(p.smem));
     if (e != cudaSuccess) return e;
     const dim3 grid{unsigned(ceil_div<int64_t>(p.n_row_tiles, p.row_tiles_per_cta)), unsigned(p.y_split), 1u};
     kern<<<grid, kCbkTmaThreads, p.smem, stream>>>(out, partial, data, perm16, offs16, nrows, ncols, nk, p.RT, p.CH,
@@ -725,7 +725,7 @@ cudaError_t launch_cols_by_key_sorted(T* out,
   do {                                                                                                  \
     auto kern = cbk_tile_kernel<T, VEC_, NV_>;                                                          \
     if (lay.total + 1024 > (size_t(48) << 10)) {                                                        \
-      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(lay.total));      \
+      e = ensure_dynamic_smem(kern, size_t(lay.total));      \
       if (e != cudaSuccess) return e;                                                                   \
     }                                                                                                   \
     kern<<<grid, kCbkTpb, lay.total, stream>>>(out, partial, data, perm16, offs16, nrows, ncols, nk,    \

@@ -14,7 +14,10 @@
 #include "row_reduce.cuh"
 #include "row_reduce_tma.cuh"
 
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 
 namespace raft_b200 {
 namespace detail {
@@ -130,9 +133,8 @@ inline int env_int(const char* name, int dflt)
   return v > 0 ? v : dflt;
 }
 
-inline Tuning tuning()
+inline Tuning read_tuning_from_env()
 {
-  // read on every call (five getenv look-ups) so that a benchmark can sweep within one process
   Tuning x;
   x.row_ctas_per_sm      = env_int("B2R_ROW_CPS", x.row_ctas_per_sm);
   x.row_chunk_threshold  = env_int("B2R_ROW_CHUNK", x.row_chunk_threshold);
@@ -155,6 +157,62 @@ inline Tuning tuning()
   if (x.row_tma_stages < 2) x.row_tma_stages = 2;
   if (x.row_tma_stages > 8) x.row_tma_stages = 8;
   return x;
+}
+
+// The knobs are read from the environment ONCE, at the first call (a call costs no getenv
+// afterwards); reload_tuning() reads them again, for a benchmark that sweeps them within one
+// process. Reloading must not run concurrently with other calls into the library.
+struct TuningCache {
+  std::atomic<bool> ready{false};
+  std::mutex lock;
+  Tuning value;
+};
+inline TuningCache& tuning_cache()
+{
+  static TuningCache c;
+  return c;
+}
+inline const Tuning& tuning()
+{
+  TuningCache& c = tuning_cache();
+  if (!c.ready.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> g(c.lock);
+    if (!c.ready.load(std::memory_order_relaxed)) {
+      c.value = read_tuning_from_env();
+      c.ready.store(true, std::memory_order_release);
+    }
+  }
+  return c.value;
+}
+inline void reload_tuning()
+{
+  TuningCache& c = tuning_cache();
+  std::lock_guard<std::mutex> g(c.lock);
+  c.value = read_tuning_from_env();
+  c.ready.store(true, std::memory_order_release);
+}
+
+// Opt-in to more than 48 KB of dynamic shared memory, remembered per (kernel, device): the driver
+// call is made only when a kernel needs more than it was granted before.
+inline cudaError_t ensure_dynamic_smem(const void* kern, size_t bytes)
+{
+  static std::mutex lock;
+  static std::unordered_map<const void*, size_t> granted[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+  std::lock_guard<std::mutex> g(lock);
+  size_t& have = granted[dev][kern];
+  if (bytes <= have) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+  if (e == cudaSuccess) have = bytes;
+  return e;
+}
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kern, size_t bytes)
+{
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(kern), bytes);
 }
 
 // Resident CTAs per SM of a kernel: the reductions launch one or two resident waves of
@@ -303,7 +361,7 @@ cudaError_t launch_row_reduce(StoreT* out,
       const size_t smem       = size_t(stages) * ((size_t(tile_rows) * row_bytes + 127) / 128 * 128);
       if (smem <= (size_t(220) << 10)) {
         auto kern      = row_reduce_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, UT, StoreT>;
-        cudaError_t ea = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        cudaError_t ea = ensure_dynamic_smem(kern, size_t(smem));
         if (ea != cudaSuccess) return ea;
         int64_t ctas = int64_t(sm_count()) * resident_ctas(kern, kTmaThreads, smem);
         int64_t rpc  = ceil_div<int64_t>(n_rows, ctas);
@@ -483,7 +541,7 @@ cudaError_t launch_col_reduce(OutT* out,
     if constexpr (V16 > 1) {
       int* cta_status = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch.get()) + p.off_status);
       auto kern       = col_partial_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16>;
-      cudaError_t ea  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(p.smem));
+      cudaError_t ea  = ensure_dynamic_smem(kern, size_t(p.smem));
       if (ea != cudaSuccess) return ea;
       kern<<<p.grid_x, kTmaThreads, p.smem, stream>>>(out, partial, data, n_rows, int(n_cols), init, inplace, main_op,
                                                      reduce_op, final_op, p.TX, p.tile_rows, p.rows_per_cta,

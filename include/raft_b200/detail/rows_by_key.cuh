@@ -472,7 +472,7 @@ cudaError_t launch_rows_by_key(SumT* sums,
 #define B2R_LAUNCH_RBK(VEC_)                                                                        \
   do {                                                                                              \
     auto kern = rows_by_key_partial_kernel<DataT, KeyT, WeightT, SumT, VEC_>;                       \
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(lay.total));    \
+    e = ensure_dynamic_smem(kern, size_t(lay.total));    \
     if (e != cudaSuccess) return e;                                                                 \
     kern<<<grid, kKeyTpb, lay.total, stream>>>(partial_sums, partial_counts, A, lda, keys, weights, \
                                                nrows, int(ncols), int(nkeys), p.kps,                \

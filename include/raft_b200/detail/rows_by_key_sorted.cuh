@@ -696,7 +696,7 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   const size_t sort_smem = rbk_sort_smem(nkeys, p.window_rows, staged);
   auto sort_kern         = staged ? rbk_sort_kernel<KeyT, true> : rbk_sort_kernel<KeyT, false>;
   if (sort_smem + 1024 > (size_t(48) << 10)) {  // static shared memory counts against the 48 KB too
-    e = cudaFuncSetAttribute(sort_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sort_smem));
+    e = ensure_dynamic_smem(sort_kern, size_t(sort_smem));
     if (e != cudaSuccess) return e;
   }
   sort_kern<<<unsigned(p.n_windows), kSortTpb, sort_smem, stream>>>(keys, nrows, nk, p.window_rows, perm, offs,

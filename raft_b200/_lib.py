@@ -63,6 +63,7 @@ SIGNATURES = {
     "b2r_apply_final": (ctypes.c_int, [_vp, _i32, _i64, _i32, _dbl, _vp]),
     "b2r_synth_fill": (ctypes.c_int, [_vp, _i32, _i64, _i64, _u64, _i32, _dbl, _dbl, _vp]),
     "b2r_trim_scratch_pool": (ctypes.c_int, []),
+    "b2r_reload_tuning": (ctypes.c_int, []),
     "b2r_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "b2r_last_cuda_error": (ctypes.c_int, []),
     "b2r_version": (ctypes.c_char_p, []),

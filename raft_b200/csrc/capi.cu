@@ -261,6 +261,12 @@ int b2r_trim_scratch_pool(void)
   return set_cuda_error(cudaMemPoolTrimTo(pool, 0));
 }
 
+int b2r_reload_tuning(void)
+{
+  detail::reload_tuning();
+  return B2R_OK;
+}
+
 const char* b2r_status_string(int status)
 {
   switch (status) {

@@ -363,6 +363,12 @@ def row_normalize(data, norm_type="L2", out=None, eps=1e-8):
     return out
 
 
+def reload_tuning():
+    """Makes the library read its B2R_* environment knobs again (they are otherwise read once, at the
+    first call). For tests and sweeps that change them within one process."""
+    L.check(L.load().b2r_reload_tuning(), "b2r_reload_tuning")
+
+
 def apply_final(v, final_op, final_scalar=1.0):
     """v[i] = final_op(v[i]) in place (the deferred final step of a sharded reduction)."""
     _require_cuda(v, "v")

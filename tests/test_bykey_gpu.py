@@ -72,10 +72,10 @@ def test_rows_by_key_skewed_and_missing_keys(cuda, oracle):
 
 
 @pytest.mark.parametrize("nobs,cols,nkeys", [(128, 32, 6), (100000, 37, 2048), (60000, 128, 1024), (512, 1024, 40)])
-def test_rows_by_key_table_algorithm(cuda, oracle, monkeypatch, nobs, cols, nkeys):
+def test_rows_by_key_table_algorithm(cuda, oracle, knobs, nobs, cols, nkeys):
     # the shared-memory-table kernel is the fallback for more keys than the sort kernel's
     # histogram holds; B2R_KEY_ALGO=1 forces it for ordinary sizes
-    monkeypatch.setenv("B2R_KEY_ALGO", "1")
+    knobs(B2R_KEY_ALGO="1")
     A, hA = device_synth((nobs, cols), np.float32, 31, "uniform", -1, 1, cuda)
     keys, hk = device_synth((nobs,), np.int32, 32, "int", 0, nkeys, cuda)
     w, hw = device_synth((nobs,), np.float32, 33, "uniform", 0, 2, cuda)
@@ -134,9 +134,9 @@ def test_cols_by_key_grid(cuda, oracle, rows, cols, nkeys, dt, tol):
 @pytest.mark.parametrize("dt,tol", [(np.float32, 1e-5), (np.float64, 1e-9)])
 @pytest.mark.parametrize("key_dt", [np.int32, np.int64])
 @pytest.mark.parametrize("staging", ["tma", "registers"])
-def test_cols_by_key_sorted_tiles(cuda, oracle, monkeypatch, rows, cols, nkeys, dt, tol, key_dt, staging):
-    monkeypatch.setenv("B2R_COLKEY_ALGO", "2")
-    monkeypatch.setenv("B2R_COLKEY_TMA", "1" if staging == "tma" else "2")
+def test_cols_by_key_sorted_tiles(cuda, oracle, knobs, rows, cols, nkeys, dt, tol, key_dt, staging):
+    knobs(B2R_COLKEY_ALGO="2")
+    knobs(B2R_COLKEY_TMA="1" if staging == "tma" else "2")
     data, hd = device_synth((rows, cols), dt, 1234, "uniform", -1, 1, cuda)
     keys, hk = device_synth((cols,), key_dt, 55, "int", 0, nkeys, cuda)
     out = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys)
@@ -150,8 +150,8 @@ def test_cols_by_key_sorted_tiles(cuda, oracle, monkeypatch, rows, cols, nkeys, 
         assert torch.equal(again, linalg.reduce_cols_by_key(data, keys, nkeys=nkeys))
 
 
-def test_cols_by_key_single_kernel_path(cuda, oracle, monkeypatch):
-    monkeypatch.setenv("B2R_COLKEY_ALGO", "1")
+def test_cols_by_key_single_kernel_path(cuda, oracle, knobs):
+    knobs(B2R_COLKEY_ALGO="1")
     data, hd = device_synth((2000, 3000), np.float32, 3, "uniform", -1, 1, cuda)
     keys, hk = device_synth((3000,), np.int32, 4, "int", 0, 77, cuda)
     out = linalg.reduce_cols_by_key(data, keys, nkeys=77)

@@ -221,12 +221,12 @@ def test_error_compensation(cuda, oracle):
 
 @pytest.mark.parametrize("rows,cols", [(100000, 64), (65537, 128), (300001, 4), (20000, 1024), (9000, 36), (70000, 256)])
 @pytest.mark.parametrize("main,red,fin", [("identity", "add", "identity"), ("sq", "add", "sqrt"), ("abs", "max", "identity")])
-def test_strided_tma_staged(cuda, oracle, monkeypatch, rows, cols, main, red, fin):
+def test_strided_tma_staged(cuda, oracle, knobs, rows, cols, main, red, fin):
     # the TMA-staged column kernel (narrow contiguous matrices), forced on; same results as the
     # register-staged kernel and within tolerance of the oracle
     t, host = device_synth((rows, cols), np.float32, 17, "uniform", -1, 1, cuda)
     plain = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin)
-    monkeypatch.setenv("B2R_COL_TMA", "1")
+    knobs(B2R_COL_TMA="1")
     staged = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin)
     ws = torch.empty(linalg.reduce_workspace_bytes(t, linalg.ALONG_COLUMNS, reduce_op=red), dtype=torch.uint8, device=cuda)
     staged_ws = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin, workspace=ws)
@@ -242,10 +242,10 @@ def test_strided_tma_staged(cuda, oracle, monkeypatch, rows, cols, main, red, fi
 
 @pytest.mark.parametrize("rows,cols", [(100000, 128), (65537, 64), (300001, 4), (20001, 500), (16384, 36), (70000, 256),
                                        (50000, 96)])
-def test_rows_tma_staged(cuda, oracle, monkeypatch, rows, cols):
+def test_rows_tma_staged(cuda, oracle, knobs, rows, cols):
     # the TMA-staged row kernel (short contiguous rows), forced on: sums, norms and argmin
     t, host = device_synth((rows, cols), np.float32, 19, "int", -4, 5, cuda)
-    monkeypatch.setenv("B2R_ROW_TMA", "1")
+    knobs(B2R_ROW_TMA="1")
     got = linalg.reduce(t, linalg.ALONG_ROWS)
     assert np.array_equal(got.cpu().numpy().astype(np.float64), host.astype(np.float64).sum(1))
     got = linalg.norm(t, "L2", linalg.ALONG_ROWS, fin_op="sqrt")
@@ -259,7 +259,7 @@ def test_rows_tma_staged(cuda, oracle, monkeypatch, rows, cols):
     assert np.array_equal(got.cpu().numpy(), np.maximum(prev.cpu().numpy(), np.abs(host).max(1)))
     tu, hu = device_synth((rows, cols), np.float32, 20, "uniform", -1, 1, cuda)
     got = linalg.reduce(tu, linalg.ALONG_ROWS)
-    monkeypatch.delenv("B2R_ROW_TMA")
+    knobs(B2R_ROW_TMA=None)
     oracle.assert_approx(oracle.reduce(hu), got.cpu().numpy(), 1e-5)
     oracle.assert_approx(linalg.reduce(tu, linalg.ALONG_ROWS).cpu().numpy(), got.cpu().numpy(), 1e-6)
 

@@ -43,19 +43,19 @@ def test_matches_regular_entry_point_twice_in_a_row(cuda, rows, cols):
     assert torch.equal(mean, linalg.reduce(a, linalg.ALONG_COLUMNS, final_op="div_const", final_scalar=float(rows)))
 
 
-def test_limit_and_bad_arguments(cuda, monkeypatch):
+def test_limit_and_bad_arguments(cuda, knobs):
     lib = L.load()
     assert lib.b2r_column_sum_f32_noalloc_max_scratch() == 1 << 20
     # a launch shape four times wider than the default needs 2368 row ranges x 128 columns of
     # fp64 partials = 2.4 MB: more than the fixed array, so the call is refused and nothing runs
     tall = torch.ones((200000, 128), dtype=torch.float32, device=cuda)
     out = torch.full((128,), 5.0, dtype=torch.float32, device=cuda)
-    monkeypatch.setenv("B2R_COL_CPS", "16")
+    knobs(B2R_COL_CPS="16")
     assert linalg.reduce_workspace_bytes(tall, linalg.ALONG_COLUMNS) > (1 << 20)
     assert _noalloc(tall, out) == L.ERR_TOO_LARGE
     torch.cuda.synchronize()
     assert torch.all(out == 5.0)
-    monkeypatch.delenv("B2R_COL_CPS")
+    knobs(B2R_COL_CPS=None)
     assert _noalloc(tall, out) == L.OK
     assert torch.all(out == 200000.0)
     small = torch.ones((8, 8), dtype=torch.float32, device=cuda)
