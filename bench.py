@@ -48,7 +48,9 @@ WORKLOADS = {
     # the callers next to the path (not baseline configs; never the default workload)
     "normalize": (100_000, 1024, "row_normalize L2 fp32 100000x1024 U[-10,10) seed 6 (read + write)"),
     "mapsum": (1_048_576, 1024, "mapThenSumReduce identity fp32, 2^30 elements U[-1,1) seed 7"),
+    "colsbykey": (2_000, 200_000, "reduce_cols_by_key fp32 2000x200000 U[-1,1) seed 8, int32 keys U[0,128) seed 9"),
 }
+COL_NKEYS = 128
 NKEYS = 1024
 
 
@@ -67,11 +69,13 @@ def algorithmic_bytes(name):
         return 2 * inp
     if name == "mapsum":
         return inp + 4
+    if name == "colsbykey":
+        return inp + cols * 4 + rows * COL_NKEYS * 4
     raise KeyError(name)
 
 
 def launches_per_step(name):
-    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 6, "normalize": 1, "mapsum": 2}[name]
+    return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 6, "normalize": 1, "mapsum": 2, "colsbykey": 3}[name]
 
 
 class Workload:
@@ -103,6 +107,10 @@ class Workload:
             linalg.synth_fill(self.data, 6, "uniform", -10, 10, first_index=base)
         elif name == "mapsum":
             linalg.synth_fill(self.data, 7, "uniform", -1, 1, first_index=base)
+        elif name == "colsbykey":
+            linalg.synth_fill(self.data, 8, "uniform", -1, 1, first_index=base)
+            self.keys = torch.empty((cols,), dtype=torch.int32, device=device)
+            linalg.synth_fill(self.keys, 9, "int", 0, COL_NKEYS)  # the columns are not sharded: same keys on every rank
         if name in ("c1", "c2", "c2sq"):
             self.out = torch.empty(rows, dtype=torch.float32, device=device)
         elif name in ("c3", "c3mean"):
@@ -116,6 +124,8 @@ class Workload:
             self.out = torch.zeros_like(self.data)
         elif name == "mapsum":
             self.out = torch.zeros(1, dtype=torch.float32, device=device)
+        elif name == "colsbykey":
+            self.out = torch.zeros((rows, COL_NKEYS), dtype=torch.float32, device=device)
         # scratch allocated once, outside the timed region (a caller-provided workspace)
         self.ws = None
         if impl == "ours":
@@ -167,6 +177,8 @@ class Workload:
                     dist.all_reduce(self.counts)  # 1024 int64 counts
             elif n == "normalize":
                 la.row_normalize(data, "L2", out=self.out)
+            elif n == "colsbykey":
+                la.reduce_cols_by_key(data, self.keys, out=self.out)
             elif n == "mapsum":
                 la.map_reduce(data, out=self.out, workspace=self.ws)
                 if self.world > 1:
@@ -195,6 +207,8 @@ class Workload:
                 st = r.row_normalize(self.out, data, "L2")
             elif n == "mapsum":
                 st = r.map_then_sum_reduce(self.out, data)
+            elif n == "colsbykey":
+                st = r.cols_by_key(self.out, data, self.keys, COL_NKEYS)
             if st != 0:
                 raise RuntimeError(f"reference wrapper status {st} for {n}")
 
@@ -300,13 +314,14 @@ def cpu_baseline(name, budget_rows=None):
     rows, cols, _ = WORKLOADS[name]
     sample_rows = min(rows, budget_rows or {"c1": 4096, "c2": 1_000_000, "c2sq": 1_000_000, "c3": 2_000_000,
                                             "c3mean": 2_000_000, "c4": 2_000_000, "c5": 1_000_000,
-                                            "normalize": 100_000, "mapsum": 262_144}[name])
+                                            "normalize": 100_000, "mapsum": 262_144, "colsbykey": 500}[name])
     seed, kind, lo, hi = {"c1": (0, "uniform", -1, 1), "c2": (1, "normal", 0, 1), "c2sq": (1, "normal", 0, 1),
                           "c3": (2, "uniform", 0, 1), "c3mean": (2, "uniform", 0, 1), "c4": (3, "int", 0, 16),
                           "c5": (4, "normal", 0, 1), "normalize": (6, "uniform", -10, 10),
-                          "mapsum": (7, "uniform", -1, 1)}[name]
+                          "mapsum": (7, "uniform", -1, 1), "colsbykey": (8, "uniform", -1, 1)}[name]
     data = o.synth((sample_rows, cols), np.float32, seed, kind, lo, hi)
     keys = o.synth((sample_rows,), np.int32, 5, "int", 0, NKEYS) if name == "c5" else None
+    ckeys = o.synth((cols,), np.int32, 9, "int", 0, COL_NKEYS) if name == "colsbykey" else None
 
     def once():
         if name == "c1":
@@ -325,6 +340,8 @@ def cpu_baseline(name, budget_rows=None):
             o.row_normalize(data, "L2")
         elif name == "mapsum":
             float(o.omp_row_sum(data).astype(np.float64).sum())  # rows in parallel, then the row sums
+        elif name == "colsbykey":
+            o.cols_by_key(data, ckeys, COL_NKEYS)
 
     once()
     reps, t0 = 0, time.perf_counter()
@@ -537,7 +554,7 @@ def main():
     line = {"metric": "hbm_gb_per_s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4", "normalize") or world == 1
+            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4", "normalize", "colsbykey") or world == 1
                                                         else "per-GPU partials + NCCL all-reduce inside the step"),
                        "l2": "L2 flushed by a 378 MB write before every step" if flush
                        else f"input {rows * cols * 4 >> 20} MB per GPU > 126 MB L2"},
@@ -558,7 +575,7 @@ def main():
         table = {}
         del w
         torch.cuda.empty_cache()
-        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5", "normalize", "mapsum"):
+        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5", "normalize", "mapsum", "colsbykey"):
             r, c, _ = WORKLOADS[cn]
             ent = {}
             for impl in ("ours", "reference"):
