@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(256) cbk_merge_kernel(T* __restrict__ out,
 // TMA-staged form of the tile kernel (rows of the matrix start on 16-byte boundaries): a producer
 // thread streams, per (row tile, chunk), the RT row pieces, the chunk's sorted offsets and its
 // segment starts into a ring of shared-memory stages with bulk asynchronous copies completing on
-// an mbarrier; kCbkConsumers threads consume the stages as above - thread (r, k) owns its table
+// an mbarrier (two CTAs per SM when the table is small); kCbkConsumers threads consume the stages as above - thread (r, k) owns its table
 // cell, so the only block-wide synchronisation is at the end of a row tile. A CTA walks a range of
 // row tiles x a range of chunks, which keeps the ring full across row tiles.
 // Every mbarrier wait is bounded; a CTA that gives up writes NaN to its outputs.
@@ -358,7 +358,7 @@ inline CbkStage cbk_stage(int RT, int CH, int offs_stride)
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kCbkTmaThreads, 1) cbk_tile_tma_kernel(T* __restrict__ out,
+__global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __restrict__ out,
                                                                        double* __restrict__ partial,
                                                                        const T* __restrict__ data,
                                                                        const unsigned short* __restrict__ perm16,
@@ -593,17 +593,31 @@ inline bool cols_by_key_sorted_supported(int64_t nrows, int64_t ncols, int64_t n
 // a row tile spans several chunks (the table is flushed once per row tile), and keys few enough
 // that a (row, key) pair finds several columns of its key in a chunk - with one column or less
 // per pair the per-pair bookkeeping dominates and shared-memory atomics are faster. Measured on
-// 1000 x 100000 fp32: 8 keys 3.6 vs 0.6 TB/s, 128 keys 2.9 vs 1.2, 2048 keys 0.7 vs 1.3; on
+// 1000 x 100000 fp32: 8 keys 3.8 vs 0.6 TB/s, 128 keys 3.2 vs 1.2, 2048 keys 0.7 vs 1.3; on
 // 4096 x 4096 with 128 keys 1.4 vs 1.7.
+// Tile geometry: RT rows (the fp64 table [RT x nkeys] within 64 KB; fewer rows when that makes a
+// key's segment in a chunk at least 8 columns long) x CH columns, 32 KB per tile.
+template <typename T>
+inline void cbk_tile_shape(int64_t nkeys, int* rt_out, int* ch_out)
+{
+  const int tile_elts = kCbkTileBytes / int(sizeof(T));
+  int RT              = kCbkMaxRT;
+  while (RT > 1 && int64_t(RT) * nkeys * int64_t(sizeof(double)) > (int64_t(64) << 10))
+    RT >>= 1;
+  while (RT > 2 && nkeys * 8 > (tile_elts / RT < 4096 ? tile_elts / RT : 4096))
+    RT >>= 1;
+  int CH = tile_elts / RT;
+  if (CH > 4096) CH = 4096;
+  *rt_out = RT;
+  *ch_out = CH;
+}
+
 template <typename T>
 inline bool cols_by_key_sorted_preferred(int64_t nrows, int64_t ncols, int64_t nkeys)
 {
   if (nrows * ncols < (int64_t(1) << 23) || ncols < 8192) return false;
-  int RT = kCbkMaxRT;
-  while (RT > 1 && int64_t(RT) * nkeys * int64_t(sizeof(double)) > (int64_t(64) << 10))
-    RT >>= 1;
-  int CH = int(kCbkTileBytes / int(sizeof(T))) / RT;
-  if (CH > 4096) CH = 4096;
+  int RT, CH;
+  cbk_tile_shape<T>(nkeys, &RT, &CH);
   return nkeys * 4 <= CH;
 }
 
@@ -612,16 +626,12 @@ inline CbkPlan plan_cols_by_key_sorted(const T* data, int64_t nrows, int64_t nco
 {
   constexpr int V16 = vec16<T>::value;
   CbkPlan p         = {};
-  // rows per tile: the fp64 table [RT x nkeys] within 64 KB, no more rows than there are
-  int RT = kCbkMaxRT;
-  while (RT > 1 && int64_t(RT) * nkeys * int64_t(sizeof(double)) > (int64_t(64) << 10))
-    RT >>= 1;
+  // no more rows per tile than there are, and chunks not much wider than the matrix
+  int RT, CH;
+  cbk_tile_shape<T>(nkeys, &RT, &CH);
   while (RT > 1 && RT / 2 >= nrows)
     RT >>= 1;
   p.RT = RT;
-  // columns per chunk: a 32 KB tile, a power of two in [256, 4096], not much wider than the matrix
-  int CH = int(kCbkTileBytes / int(sizeof(T))) / RT;
-  if (CH > 4096) CH = 4096;
   while (CH > 256 && CH / 2 >= ncols)
     CH >>= 1;
   p.CH          = CH;
@@ -634,7 +644,9 @@ inline CbkPlan plan_cols_by_key_sorted(const T* data, int64_t nrows, int64_t nco
   const CbkStage stage = cbk_stage<T>(RT, CH, p.offs_stride);
   const size_t cells   = size_t(RT) * nkeys;
   p.acc_bytes          = align_up((cells < size_t(kCbkConsumers) ? size_t(kCbkConsumers) : cells) * sizeof(double), 128);
-  int stages           = int(((size_t(220) << 10) - p.acc_bytes) / stage.bytes);
+  // two CTAs per SM when the table is small: more warps to hide the gather's latencies
+  const int ctas_per_sm = p.acc_bytes + 2 * stage.bytes <= (size_t(110) << 10) ? 2 : 1;
+  int stages            = int(((size_t(220) << 10) / ctas_per_sm - p.acc_bytes) / stage.bytes);
   if (stages > kCbkMaxStages) stages = kCbkMaxStages;
   p.stages = stages;
   p.tma    = tuning().colkey_tma == 1 && p.vec > 1 && stages >= 2;
@@ -642,13 +654,14 @@ inline CbkPlan plan_cols_by_key_sorted(const T* data, int64_t nrows, int64_t nco
     p.smem = p.acc_bytes + size_t(stages) * stage.bytes;
     // the split that needs the fewest waves of (SMs) CTAs; splitting the columns costs a merge
     int64_t best_cost = 0;
-    for (int y = 1; y <= 2 * sms && y <= p.n_chunks; ++y) {
+    const int slots_total = sms * ctas_per_sm;
+    for (int y = 1; y <= 2 * slots_total && y <= p.n_chunks; ++y) {
       const int cpc      = int(ceil_div<int64_t>(p.n_chunks, y));
       const int ys       = int(ceil_div<int64_t>(p.n_chunks, cpc));
-      const int64_t per_x = p.n_row_tiles * ys > sms ? ceil_div<int64_t>(p.n_row_tiles * ys, sms) : 1;
+      const int64_t per_x = p.n_row_tiles * ys > slots_total ? ceil_div<int64_t>(p.n_row_tiles * ys, slots_total) : 1;
       const int64_t rtpc  = per_x < p.n_row_tiles ? per_x : p.n_row_tiles;  // row tiles per CTA
       const int64_t gx    = ceil_div<int64_t>(p.n_row_tiles, rtpc);
-      const int64_t waves = ceil_div<int64_t>(gx * ys, sms);
+      const int64_t waves = ceil_div<int64_t>(gx * ys, slots_total);
       const int64_t cost  = waves * rtpc * cpc * (ys > 1 ? 51 : 50) + (ys > 1 ? 50 : 0);
       if (best_cost == 0 || cost < best_cost) {
         best_cost           = cost;
