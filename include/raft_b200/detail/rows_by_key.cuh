@@ -31,6 +31,7 @@
 #include "common.cuh"
 #include "launch.cuh"
 #include "ops.cuh"
+#include "rows_by_key_small.cuh"
 #include "rows_by_key_sorted.cuh"
 
 namespace raft_b200 {
@@ -406,6 +407,7 @@ template <typename DataT, typename SumT>
 inline size_t rows_by_key_scratch_bytes(const DataT* A, int64_t lda, int64_t nrows, int64_t ncols, int64_t nkeys)
 {
   if (nrows <= 0 || ncols <= 0 || nkeys <= 0) return 0;
+  if (tuning().key_algo == 0 && rows_by_key_small_supported(nrows, ncols, nkeys)) return 0;  // one launch, no scratch
   if (tuning().key_algo != 1 && rows_by_key_sorted_supported(nrows, ncols, nkeys))
     return plan_rows_by_key_sorted<DataT>(A, lda, nrows, ncols, nkeys,
                                           sizeof(typename sum_state<SumT>::type::carry_t)).total;
@@ -439,6 +441,10 @@ cudaError_t launch_rows_by_key(SumT* sums,
     }
     return cudaSuccess;
   }
+  // small inputs: one launch (key_algo 0 = by size; 1 = shared-memory table, 2 = sorted pipeline, forced)
+  if (tuning().key_algo == 0 && rows_by_key_small_supported(nrows, ncols, nkeys))
+    return launch_rows_by_key_small<DataT, KeyT, WeightT, SumT>(sums, counts, A, lda, keys, weights, nrows, ncols,
+                                                                nkeys, reset, stream);
   if (tuning().key_algo != 1 && rows_by_key_sorted_supported(nrows, ncols, nkeys))
     return launch_rows_by_key_sorted<DataT, KeyT, WeightT, SumT>(sums, counts, A, lda, keys, weights, nrows, ncols,
                                                                  nkeys, reset, stream, ws);

@@ -17,6 +17,8 @@ unsupported type / operator combinations raise B2RError (raft::exception in the 
 Functors are named by strings because a C ABI cannot carry a device lambda; the C++ headers
 under include/raft/ accept arbitrary functors.
 """
+import contextlib
+
 import torch
 
 from . import _lib as L
@@ -48,8 +50,23 @@ def _as_int(v):
         return 0
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_NO_SWITCH = contextlib.nullcontext()
+
+
 def _stream_ptr(device):
+    """cudaStream_t of torch's current stream on `device`."""
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def _on(device):
+    """Context that makes `device` current - a no-op object when it already is (the usual case; switching
+    costs microseconds that small reductions notice)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
 
 
 def _layout_of(data):
@@ -147,7 +164,7 @@ def reduce(data, apply=ALONG_ROWS, dots=None, init=0.0, inplace=False, main_op="
     ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None \
         else (None, 0)
     lib = L.load()
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         st = lib.b2r_reduce(desc, dots.data_ptr(), data.data_ptr(), ws_ptr, ws_bytes, _stream_ptr(data.device))
     L.check(st, "b2r_reduce")
     return dots
@@ -159,7 +176,7 @@ def reduce_workspace_bytes(data, apply=ALONG_ROWS, reduce_op="add", out_dtype=No
     out_dt = _KVP_OF[in_dt] if reduce_op in ("argmin", "argmax") else _DTYPES[out_dtype or data.dtype]
     desc = L.ReduceDesc(in_dtype=in_dt, out_dtype=out_dt, layout=layout, apply=apply, n_rows=n_rows, n_cols=n_cols,
                         reduce_op=_REDUCE[reduce_op])
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         return L.load().b2r_reduce_workspace_bytes(desc, data.data_ptr())
 
 
@@ -196,7 +213,7 @@ def norm(data, norm_type="L2", apply=ALONG_ROWS, out=None, fin_op="identity", fi
                          ("rows" if apply == ALONG_ROWS else "columns"))
     ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None \
         else (None, 0)
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         st = L.load().b2r_norm(_NORM[norm_type], apply, layout, _DTYPES[data.dtype], _DTYPES[out.dtype], n_rows,
                                n_cols, _FINAL[fin_op], float(final_scalar), out.data_ptr(), data.data_ptr(), ws_ptr,
                                ws_bytes, _stream_ptr(data.device))
@@ -242,7 +259,7 @@ def reduce_rows_by_key(d_A, d_keys, n_unique_keys, d_sums=None, d_weights=None, 
         raise L.B2RError(L.ERR_UNSUPPORTED, "reduce_rows_by_key")
     ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None \
         else (None, 0)
-    with torch.cuda.device(d_A.device):
+    with _on(d_A.device):
         st = L.load().b2r_reduce_rows_by_key(
             d_sums.data_ptr(), counts.data_ptr() if counts is not None else None, d_A.data_ptr(), lda,
             d_keys.data_ptr(), d_weights.data_ptr() if d_weights is not None else None, _DTYPES[d_A.dtype], key_dt,
@@ -253,7 +270,7 @@ def reduce_rows_by_key(d_A, d_keys, n_unique_keys, d_sums=None, d_weights=None, 
 
 def reduce_rows_by_key_workspace_bytes(d_A, n_unique_keys, lda=None):
     nrows, ncols = d_A.shape
-    with torch.cuda.device(d_A.device):
+    with _on(d_A.device):
         return L.load().b2r_reduce_rows_by_key_workspace_bytes(d_A.data_ptr(), lda or ncols, _DTYPES[d_A.dtype],
                                                                nrows, ncols, n_unique_keys)
 
@@ -282,7 +299,7 @@ def reduce_cols_by_key(data, keys, out=None, nkeys=0, reset_sums=True):
     key_dt = _KEY_DTYPES.get(keys.dtype)
     if key_dt is None or data.dtype not in (torch.float32, torch.float64) or out.dtype != data.dtype:
         raise L.B2RError(L.ERR_UNSUPPORTED, "reduce_cols_by_key")
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         st = L.load().b2r_reduce_cols_by_key(out.data_ptr(), data.data_ptr(), keys.data_ptr(), _DTYPES[data.dtype],
                                              key_dt, nrows, ncols, nkeys, 1 if reset_sums else 0,
                                              _stream_ptr(data.device))
@@ -301,7 +318,7 @@ def _matrix_arg(fn_name, data, out, index_dtype):
         raise ValueError("Size of output vector must equal number of rows in input matrix.")
     if data.dtype not in (torch.float32, torch.float64) or out.dtype not in (torch.int32, torch.int64):
         raise L.B2RError(L.ERR_UNSUPPORTED, fn_name)
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         st = getattr(L.load(), fn_name)(out.data_ptr(), _DTYPES[out.dtype], data.data_ptr(), _DTYPES[data.dtype],
                                         n_rows, n_cols, _stream_ptr(data.device))
     L.check(st, fn_name)
@@ -356,7 +373,7 @@ def row_normalize(data, norm_type="L2", out=None, eps=1e-8):
     if norm_type not in ("L1", "L2", "Linf"):
         raise ValueError("Unsupported norm type: %s" % norm_type)
     n_rows, n_cols = data.shape
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         st = L.load().b2r_row_normalize(out.data_ptr(), data.data_ptr(), _DTYPES[data.dtype], n_rows, n_cols,
                                         _NORM[norm_type], float(eps), _stream_ptr(data.device))
     L.check(st, "b2r_row_normalize")
@@ -372,7 +389,7 @@ def reload_tuning():
 def apply_final(v, final_op, final_scalar=1.0):
     """v[i] = final_op(v[i]) in place (the deferred final step of a sharded reduction)."""
     _require_cuda(v, "v")
-    with torch.cuda.device(v.device):
+    with _on(v.device):
         st = L.load().b2r_apply_final(v.data_ptr(), _DTYPES[v.dtype], v.numel(), _FINAL[final_op],
                                       float(final_scalar), _stream_ptr(v.device))
     L.check(st, "b2r_apply_final")
@@ -386,7 +403,7 @@ def synth_fill(dst, seed, kind, lo=0.0, hi=1.0, first_index=0):
     if not dst.is_contiguous():
         raise ValueError("dst must be contiguous")
     k = {"uniform": 0, "normal": 1, "int": 2}[kind]
-    with torch.cuda.device(dst.device):
+    with _on(dst.device):
         st = L.load().b2r_synth_fill(dst.data_ptr(), _DTYPES[dst.dtype], dst.numel(), first_index, seed, k,
                                      float(lo), float(hi), _stream_ptr(dst.device))
     L.check(st, "b2r_synth_fill")

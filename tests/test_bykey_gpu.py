@@ -43,7 +43,7 @@ def test_rows_by_key_grid(cuda, oracle, nobs, cols, nkeys, dt, tol, weighted, ke
 
 
 def test_rows_by_key_lda_and_workspace(cuda, oracle):
-    nobs, cols, lda, nkeys = 7001, 48, 64, 200
+    nobs, cols, lda, nkeys = 70001, 48, 64, 200  # above the one-launch kernel's row limit: scratch is needed
     full, hfull = device_synth((nobs, lda), np.float32, 9, "normal", 0, 1, cuda)
     keys, hk = device_synth((nobs,), np.int32, 10, "int", 0, nkeys, cuda)
     A = full[:, :cols]  # row stride 64, 48 used columns
@@ -69,6 +69,42 @@ def test_rows_by_key_skewed_and_missing_keys(cuda, oracle):
     esum, ecnt = oracle.rows_by_key(hA, hk, nkeys)
     oracle.assert_approx(esum, sums.cpu().numpy(), 1e-5)
     assert np.array_equal(counts.cpu().numpy(), ecnt)
+
+
+@pytest.mark.parametrize("nobs,cols,nkeys,dt,tol", [(128, 32, 6, np.float32, 1e-6), (512, 1024, 40, np.float64, 1e-9),
+                                                    (20000, 128, 1024, np.float32, 1e-5), (5000, 4, 7, np.float32, 1e-5),
+                                                    (3000, 130, 300, np.float64, 1e-9), (32768, 64, 3, np.float32, 1e-5)])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_rows_by_key_sorted_pipeline_on_small_inputs(cuda, oracle, knobs, nobs, cols, nkeys, dt, tol, weighted):
+    """Inputs of up to 32768 rows take the one-launch kernel by default; the six-kernel sorted pipeline must give
+    the same answers on them."""
+    knobs(B2R_KEY_ALGO="2")
+    A, hA = device_synth((nobs, cols), dt, 1234, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((nobs,), np.int32, 4321, "int", 0, nkeys, cuda)
+    w, hw = device_synth((nobs,), dt, 77, "uniform", 0, 2, cuda) if weighted else (None, None)
+    counts = torch.empty(nkeys, dtype=torch.int64, device=cuda)
+    sums = linalg.reduce_rows_by_key(A, keys, nkeys, d_weights=w, counts=counts)
+    esum, ecnt = oracle.rows_by_key(hA, hk, nkeys, weights=hw)
+    oracle.assert_approx(esum, sums.cpu().numpy(), tol, "sorted pipeline")
+    assert np.array_equal(counts.cpu().numpy(), ecnt)
+
+
+@pytest.mark.parametrize("nobs,cols,nkeys", [(10000, 128, 64), (10000, 128, 4096), (32768, 128, 1), (32768, 36, 70000),
+                                             (1, 5, 3), (9999, 1000, 17), (200, 8, 200)])
+def test_rows_by_key_one_launch_kernel(cuda, oracle, nobs, cols, nkeys):
+    """Shapes aimed at the one-launch kernel: the reference's smallest bench shapes
+    (bench/prims/linalg/reduce_rows_by_key.cu:55-72), one key for all rows, far more keys than rows, one row."""
+    A, hA = device_synth((nobs, cols), np.float32, 12, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((nobs,), np.int32, 13, "int", 0, nkeys, cuda)
+    counts = torch.empty(nkeys, dtype=torch.int64, device=cuda)
+    sums = linalg.reduce_rows_by_key(A, keys, nkeys, counts=counts)
+    assert linalg.reduce_rows_by_key_workspace_bytes(A, nkeys) == 0
+    esum, ecnt = oracle.rows_by_key(hA, hk, nkeys)
+    oracle.assert_approx(esum, sums.cpu().numpy(), 1e-5, "one launch")
+    assert np.array_equal(counts.cpu().numpy(), ecnt)
+    linalg.reduce_rows_by_key(A, keys, nkeys, d_sums=sums, reset_sums=False, counts=counts)
+    oracle.assert_approx(2 * esum, sums.cpu().numpy(), 2e-5, "accumulate")
+    assert np.array_equal(counts.cpu().numpy(), 2 * ecnt)
 
 
 @pytest.mark.parametrize("nobs,cols,nkeys", [(128, 32, 6), (100000, 37, 2048), (60000, 128, 1024), (512, 1024, 40)])
