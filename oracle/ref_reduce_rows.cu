@@ -25,10 +25,7 @@ REF_EXPORT int ref_reduce_contiguous(const b2r_reduce_desc* d, void* out, const 
   const bool rm = d->layout == B2R_ROW_MAJOR;
   if (d->in_dtype == B2R_F32 && d->out_dtype == B2R_F32)
     return rm ? dispatch<true, true, float>(*d, out, in, s) : dispatch<false, false, float>(*d, out, in, s);
-  if (d->in_dtype == B2R_F64 && d->out_dtype == B2R_F64) {
-    if (d->main_op == B2R_MAIN_SQ && d->reduce_op == B2R_REDUCE_ADD && d->final_op == B2R_FINAL_SQRT)
-      return rm ? run<true, true, double, double>(*d, out, in, d->init, raft::sq_op{}, raft::add_op{}, raft::sqrt_op{}, s)
-                : run<false, false, double, double>(*d, out, in, d->init, raft::sq_op{}, raft::add_op{}, raft::sqrt_op{}, s);
-  }
+  if (d->in_dtype == B2R_F64 && d->out_dtype == B2R_F64)
+    return rm ? dispatch<true, true, double>(*d, out, in, s) : dispatch<false, false, double>(*d, out, in, s);
   return B2R_ERR_UNSUPPORTED;
 }

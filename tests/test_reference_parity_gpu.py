@@ -116,3 +116,19 @@ def test_cols_by_key_against_reference(cuda, oracle, ref, rows, cols, nkeys):
     exp = oracle.cols_by_key(hd, hk, nkeys)
     oracle.assert_approx(exp, theirs.cpu().numpy(), 1e-3, "reference vs oracle")
     oracle.assert_approx(theirs.cpu().numpy(), ours.cpu().numpy(), 1e-3, "ours vs reference")
+
+
+@pytest.mark.parametrize("main,red,fin", [("identity", "add", "identity"), ("sq", "add", "sqrt"), ("abs", "max", "identity")])
+@pytest.mark.parametrize("rows,cols", [(1234, 33), (1000, 500), (9, 33333)])
+@pytest.mark.parametrize("apply", [0, 1])
+def test_double_precision_against_reference(cuda, oracle, ref, main, red, fin, rows, cols, apply):
+    t, host = device_synth((rows, cols), np.float64, 4321, "uniform", -1, 1, cuda)
+    n_out = rows if apply == L.ALONG_ROWS else cols
+    theirs = torch.empty(n_out, dtype=torch.float64, device=cuda)
+    assert ref.reduce(t, apply, theirs, main_op=ENUM[main], reduce_op=ENUM[red], final_op=ENUM[fin]) == 0
+    ours = linalg.reduce(t, apply, main_op=main, reduce_op=red, final_op=fin)
+    exp = oracle.reduce(host, apply=apply, main_op=main, reduce_op=red, final_op=fin)
+    oracle.assert_approx(exp, theirs.cpu().numpy(), 1e-9, "reference vs oracle")
+    oracle.assert_approx(theirs.cpu().numpy(), ours.cpu().numpy(), 1e-9, "ours vs reference")
+    if red == "max":
+        assert torch.equal(ours, theirs)
