@@ -4,7 +4,7 @@
 # the small C ABI of oracle/ref_*.cu. Test infrastructure: used to validate the CPU oracle and
 # as the "reference" column of the benchmark.
 #
-#   oracle/build_ref.sh [reference checkout, default /root/reference]
+#   oracle/build_ref.sh [path of the reference checkout; default: REF below]
 #
 # The reference's cmake build cannot configure offline (it fetches rapids-cmake, rmm,
 # rapids_logger, gtest), but this path is header-only; it needs
