@@ -11,6 +11,7 @@
 
 #include "col_reduce.cuh"
 #include "col_reduce_tma.cuh"
+#include "col_reduce_tma2d.cuh"
 #include "row_reduce.cuh"
 #include "row_reduce_tma.cuh"
 
@@ -119,6 +120,7 @@ struct Tuning {
   int colkey_tma           = 1;     // B2R_COLKEY_TMA 1: TMA-staged ring for the sorted column tiles, 2: off
   int col_tma              = 1;     // B2R_COL_TMA    1: TMA-staged tiles for narrow contiguous column reductions, 2: off
   int col_tma_tile_kb      = 32;    // B2R_COL_TMA_KB tile size of the TMA ring, KiB
+  int col_tma2d_min_mb     = 256;   // B2R_COL_TMA2D_MB smallest matrix (MiB) for the tiled-TMA kernel of wide matrices
   int tma_stages           = 4;     // B2R_TMA_STAGES stages of the TMA ring (2..8)
   int row_tma              = 0;     // B2R_ROW_TMA    1: TMA-staged tiles for short contiguous rows
   int row_tma_tile_kb      = 16;    // B2R_ROW_TMA_KB tile size of the row kernel's TMA ring, KiB
@@ -148,6 +150,7 @@ inline Tuning read_tuning_from_env()
   x.colkey_tma           = env_int("B2R_COLKEY_TMA", x.colkey_tma);
   x.col_tma              = env_int("B2R_COL_TMA", x.col_tma);
   x.col_tma_tile_kb      = env_int("B2R_COL_TMA_KB", x.col_tma_tile_kb);
+  x.col_tma2d_min_mb     = env_int("B2R_COL_TMA2D_MB", x.col_tma2d_min_mb);
   x.tma_stages           = env_int("B2R_TMA_STAGES", x.tma_stages);
   if (x.tma_stages < 2) x.tma_stages = 2;
   if (x.tma_stages > 8) x.tma_stages = 8;
@@ -424,6 +427,7 @@ cudaError_t launch_row_reduce(StoreT* out,
 // ---------------------------------------------------------------------------------------
 struct ColPlan {
   bool tma;          // TMA-staged kernel (narrow, contiguous rows)
+  bool tma2d;        // tiled-TMA kernel (wide matrices): grid_x column blocks x grid_y row ranges
   int tile_rows;     // rows per TMA tile
   int stages;        // stages of the TMA ring
   size_t off_status; // byte offset of the per-CTA status words inside the scratch
@@ -466,6 +470,8 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
   p.smem         = size_t(TPB) * p.vec * sizeof(State);
   p.scratch      = gy > 1 ? align_up(size_t(gy) * size_t(n_cols) * sizeof(typename State::carry_t), 256) : 0;
   p.tma          = false;
+  p.tma2d        = false;
+  p.stages       = 0;
   p.tile_rows    = 0;
   p.off_status   = 0;
   // TMA-staged variant: rows contiguous, the whole width in one CTA, enough rows to stream
@@ -494,6 +500,45 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
     const size_t need = parts + align_up(size_t(ctas) * sizeof(int), 256);
     p.scratch    = p.scratch > need ? p.scratch : need;
     p.tma        = ctas > 1 && p.smem <= (size_t(220) << 10);
+  }
+  // tiled-TMA variant: wide matrices (more than one 32-vector column block), 16-byte aligned rows,
+  // and enough data that filling the rings pays (measured: on par with the register-staged kernel
+  // at 256 MB, 5-6 % faster for fp32 and 10-23 % for fp64 in the GB range)
+  if constexpr (tensor_map_dtype<InT>::supported) {
+    const int64_t BX = int64_t(32) * V16;
+    if (!p.tma && tuning().col_tma == 1 && vec_ok && V16 > 1 && n_cols > BX && n_rows >= 4096 &&
+        n_rows < (int64_t(1) << 31) && n_cols < (int64_t(1) << 31) && (size_t(ld) * sizeof(InT)) % 16 == 0 &&
+        size_t(n_rows) * size_t(n_cols) * sizeof(InT) >= (size_t(tuning().col_tma2d_min_mb) << 20)) {
+      const int64_t gx  = ceil_div<int64_t>(n_cols, BX);
+      const int sms     = sm_count();
+      int64_t best_gy = 0, best_cost = 0;
+      const int64_t max_gy = n_rows / (4 * kBoxRows);  // at least four boxes per CTA
+      // at most four CTAs per SM in all, like the register-staged kernel: the partial rows stay
+      // within a few hundred KB whatever the shape
+      for (int64_t gy = 2; gy <= max_gy && gx * gy <= int64_t(4) * sms; ++gy) {
+        int64_t rpc         = ceil_div<int64_t>(ceil_div<int64_t>(n_rows, gy), kBoxRows) * kBoxRows;
+        const int64_t gy_r  = ceil_div<int64_t>(n_rows, rpc);
+        const int64_t waves = ceil_div<int64_t>(gx * gy_r, sms);
+        const int64_t cost  = waves * (rpc + 2 * kBoxRows);  // per-CTA ramp-up of about two boxes
+        if (best_gy == 0 || cost < best_cost) {
+          best_gy   = gy_r;
+          best_cost = cost;
+        }
+      }
+      if (best_gy >= 2) {
+        int64_t rpc    = ceil_div<int64_t>(ceil_div<int64_t>(n_rows, best_gy), kBoxRows) * kBoxRows;
+        p.grid_x       = unsigned(gx);
+        p.grid_y       = unsigned(ceil_div<int64_t>(n_rows, rpc));
+        p.rows_per_cta = rpc;
+        p.stages       = 4;
+        p.smem         = size_t(p.stages) * size_t(kBoxRows) * size_t(BX) * sizeof(InT) +
+                 size_t(kTmaConsumers / 32) * size_t(BX) * sizeof(State);
+        const size_t parts = align_up(size_t(p.grid_y) * size_t(n_cols) * sizeof(typename State::carry_t), 256);
+        p.off_status       = parts;
+        p.scratch          = parts + align_up(size_t(p.grid_y) * sizeof(int), 256);
+        p.tma2d            = p.grid_y >= 2 && p.smem <= (size_t(220) << 10);
+      }
+    }
   }
   return p;
 }
@@ -552,6 +597,31 @@ cudaError_t launch_col_reduce(OutT* out,
       col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin, TPB, 0, stream>>>(
         out, partial, int(p.grid_x), n_cols, init, inplace, reduce_op, final_op, cta_status);
       return cudaGetLastError();
+    }
+  }
+  if (p.tma2d) {
+    if constexpr (V16 > 1 && tensor_map_dtype<InT>::supported) {
+      CUtensorMap tmap;
+      cudaError_t ea = make_tensor_map_2d<InT>(&tmap, data, n_rows, n_cols, ld, kBoxRows, 32 * V16);
+      if (ea == cudaSuccess) {
+        int* cta_status = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch.get()) + p.off_status);
+        ea              = cudaMemsetAsync(cta_status, 0, size_t(p.grid_y) * sizeof(int), stream);
+        if (ea != cudaSuccess) return ea;
+        auto kern = col_partial_tma2d_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16>;
+        ea        = ensure_dynamic_smem(kern, size_t(p.smem));
+        if (ea != cudaSuccess) return ea;
+        const dim3 grid2(p.grid_x, p.grid_y);
+        kern<<<grid2, kTmaThreads, p.smem, stream>>>(out, partial, tmap, n_rows, n_cols, init, inplace, main_op,
+                                                    reduce_op, final_op, p.rows_per_cta, p.stages, cta_status);
+        ea = cudaGetLastError();
+        if (ea != cudaSuccess) return ea;
+        const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));
+        col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin, TPB, 0, stream>>>(
+          out, partial, int(p.grid_y), n_cols, init, inplace, reduce_op, final_op, cta_status);
+        return cudaGetLastError();
+      }
+      // no tensor map (driver entry point missing): the register-staged kernel below uses the same
+      // scratch layout [row ranges][n_cols]
     }
   }
   const dim3 grid(p.grid_x, p.grid_y);

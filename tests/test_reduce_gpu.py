@@ -240,6 +240,40 @@ def test_strided_tma_staged(cuda, oracle, knobs, rows, cols, main, red, fin):
     oracle.assert_approx(oracle.reduce(hd, apply=1, main_op=main, reduce_op=red, final_op=fin), got.cpu().numpy(), 1e-9)
 
 
+@pytest.mark.parametrize("rows,cols,dt", [(5000, 300, np.float32), (4100, 132, np.float32), (20000, 1024, np.float32),
+                                          (9000, 2052, np.float32), (70000, 256, np.float32), (6000, 130, np.float64),
+                                          (12345, 1000, np.float64), (8192, 520, np.float16), (5000, 260, np.int32)])
+@pytest.mark.parametrize("main,red,fin", [("identity", "add", "identity"), ("sq", "add", "sqrt"), ("abs", "max", "identity")])
+def test_strided_tiled_tma(cuda, oracle, knobs, rows, cols, dt, main, red, fin):
+    """The tiled-TMA kernel of wide matrices (cp.async.bulk.tensor.2d), forced onto small shapes: ragged last
+    column block, ragged last box of a row range, 16 / 8 / 4 / 2-byte elements, every state type."""
+    if dt == np.int32 and fin == "sqrt":
+        pytest.skip("no root of an integer sum")
+    knobs(B2R_COL_TMA2D_MB="1")
+    kind, lo, hi = ("int", -3, 4) if dt == np.int32 else ("uniform", -1, 1)
+    t, host = device_synth((rows, cols), dt, 23, kind, lo, hi, cuda)
+    if rows * cols * t.element_size() < (1 << 20):
+        pytest.skip("below the smallest size the knob can force")
+    out_dt = torch.float32 if dt == np.float16 else None
+    got = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin, out_dtype=out_dt)
+    exp = oracle.reduce(host, apply=1, main_op=main, reduce_op=red, final_op=fin)
+    oracle.assert_approx(exp, got.cpu().numpy(), 1e-9 if dt == np.float64 else 1e-5, "tiled TMA")
+    knobs(B2R_COL_TMA="2")  # register-staged kernel: same partial layout, same answers
+    ldg = linalg.reduce(t, linalg.ALONG_COLUMNS, main_op=main, reduce_op=red, final_op=fin, out_dtype=out_dt)
+    oracle.assert_approx(ldg.cpu().numpy(), got.cpu().numpy(), 1e-12 if dt == np.float64 else 1e-6, "vs register-staged")
+    if red == "max" or dt == np.int32:
+        assert torch.equal(got, ldg)
+
+
+def test_strided_tiled_tma_full_size(cuda):
+    """300 000 x 1024 fp32 (1.2 GB, default policy): integer-valued data, so every column sum is exact."""
+    t, host = device_synth((300000, 1024), np.float32, 31, "int", 0, 16, cuda)
+    got = linalg.reduce(t, linalg.ALONG_COLUMNS)
+    assert np.array_equal(got.cpu().numpy().astype(np.int64), host.sum(axis=0, dtype=np.int64))
+    mean = linalg.reduce(t, linalg.ALONG_COLUMNS, final_op="div_const", final_scalar=300000.0)
+    assert np.allclose(mean.cpu().numpy(), host.mean(axis=0, dtype=np.float64), rtol=1e-6, atol=0)
+
+
 @pytest.mark.parametrize("rows,cols", [(100000, 128), (65537, 64), (300001, 4), (20001, 500), (16384, 36), (70000, 256),
                                        (50000, 96)])
 def test_rows_tma_staged(cuda, oracle, knobs, rows, cols):
