@@ -115,7 +115,7 @@ struct Tuning {
   int split_ctas_per_sm    = 4;   // B2R_SPLIT_CPS
   int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
-  int key_algo             = 0;     // B2R_KEY_ALGO   0: by size (one-launch kernel up to 32768 rows), 1: shared-memory table, 2: sort then stream
+  int key_algo             = 0;     // B2R_KEY_ALGO   0: by size, 1: shared-memory table, 2: sort then stream, 3: one-launch kernel (<= 32768 rows)
   int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted column tiles
   int colkey_tma           = 1;     // B2R_COLKEY_TMA 1: TMA-staged ring for the sorted column tiles, 2: off
   int col_tma              = 1;     // B2R_COL_TMA    1: TMA-staged tiles for narrow contiguous column reductions, 2: off

@@ -407,7 +407,10 @@ template <typename DataT, typename SumT>
 inline size_t rows_by_key_scratch_bytes(const DataT* A, int64_t lda, int64_t nrows, int64_t ncols, int64_t nkeys)
 {
   if (nrows <= 0 || ncols <= 0 || nkeys <= 0) return 0;
-  if (tuning().key_algo == 0 && rows_by_key_small_supported(nrows, ncols, nkeys)) return 0;  // one launch, no scratch
+  if (rows_by_key_small_supported(nrows, ncols, nkeys) &&
+      (tuning().key_algo == 3 ||
+       (tuning().key_algo == 0 && rows_by_key_small_preferred(nrows, ncols, nkeys, sizeof(DataT)))))
+    return 0;  // one launch, no scratch
   if (tuning().key_algo != 1 && rows_by_key_sorted_supported(nrows, ncols, nkeys))
     return plan_rows_by_key_sorted<DataT>(A, lda, nrows, ncols, nkeys,
                                           sizeof(typename sum_state<SumT>::type::carry_t)).total;
@@ -441,8 +444,11 @@ cudaError_t launch_rows_by_key(SumT* sums,
     }
     return cudaSuccess;
   }
-  // small inputs: one launch (key_algo 0 = by size; 1 = shared-memory table, 2 = sorted pipeline, forced)
-  if (tuning().key_algo == 0 && rows_by_key_small_supported(nrows, ncols, nkeys))
+  // small inputs: one launch (key_algo 0 = by size; forced: 1 = shared-memory table, 2 = sorted pipeline,
+  // 3 = one-launch kernel)
+  if (rows_by_key_small_supported(nrows, ncols, nkeys) &&
+      (tuning().key_algo == 3 ||
+       (tuning().key_algo == 0 && rows_by_key_small_preferred(nrows, ncols, nkeys, sizeof(DataT)))))
     return launch_rows_by_key_small<DataT, KeyT, WeightT, SumT>(sums, counts, A, lda, keys, weights, nrows, ncols,
                                                                 nkeys, reset, stream);
   if (tuning().key_algo != 1 && rows_by_key_sorted_supported(nrows, ncols, nkeys))

@@ -207,6 +207,15 @@ __global__ void __launch_bounds__(kSmallTpb) rbk_small_kernel(SumT* __restrict__
   }
 }
 
+// One CTA adds up ALL rows of its keys: fine while that is about a megabyte per CTA (ranges of keys
+// go to at most one CTA per SM); beyond that - few keys or long rows - the sorted pipeline spreads
+// the rows of a key over many warps and wins although it needs six launches.
+inline bool rows_by_key_small_preferred(int64_t nrows, int64_t ncols, int64_t nkeys, size_t elem_size)
+{
+  const int64_t ctas = nkeys < sm_count() ? nkeys : sm_count();
+  return nrows * ncols * int64_t(elem_size) <= ctas * (int64_t(1) << 20);
+}
+
 inline bool rows_by_key_small_supported(int64_t nrows, int64_t ncols, int64_t nkeys)
 {
   // keys per CTA are staged as 16-bit values too (0xffff = not this CTA's key)

@@ -282,6 +282,7 @@ __global__ void __launch_bounds__(256) rbk_stream_kernel(typename sum_state<SumT
                                                         int n_groups,
                                                         int max_units,
                                                         int G,
+                                                        int col_split,
                                                         const unsigned* __restrict__ perm,
                                                         const int* __restrict__ offs,
                                                         const int* __restrict__ uoffs,
@@ -300,12 +301,18 @@ __global__ void __launch_bounds__(256) rbk_stream_kernel(typename sum_state<SumT
   const int grp  = lane >> lg;
   const int gpw  = 32 >> lg;
   const int nvec = ncols / VEC;  // VEC divides ncols on the vector path
-  const int64_t total_slots = int64_t(n_groups) * max_units;
+  // a queue item is (unit, part of the columns): with few rows but long ones the columns of a unit
+  // are cut into col_split parts, so that there are enough items for every warp
+  const int64_t total_items = int64_t(n_groups) * max_units * col_split;
+  const int passes          = (nvec + G - 1) / G;
+  const int passes_per_part = (passes + col_split - 1) / col_split;
   while (true) {
-    long long slot = 0;
-    if (lane == 0) slot = atomicAdd(unit_counter, 1);
-    slot = __shfl_sync(0xffffffffu, slot, 0);
-    if (slot >= total_slots) break;
+    long long item = 0;
+    if (lane == 0) item = atomicAdd(unit_counter, 1);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= total_items) break;
+    const long long slot = col_split > 1 ? item / col_split : item;
+    const int part       = col_split > 1 ? int(item - slot * col_split) : 0;
     const int g = int(slot / max_units);
     const int u = int(slot - int64_t(g) * max_units);
     if (u >= uoffs[size_t(g) * (nkeys + 1) + nkeys]) continue;  // this group has fewer units
@@ -345,7 +352,10 @@ __global__ void __launch_bounds__(256) rbk_stream_kernel(typename sum_state<SumT
       return in_win + gperm[in_win + unsigned(w_beg + (o - (w_end - w_cnt)))];
     };
     CarryT* dst = partial + size_t(slot) * ncols;
-    for (int cv0 = 0; cv0 < nvec; cv0 += G) {
+    const int cv_beg = part * passes_per_part * G;
+    int cv_end       = cv_beg + passes_per_part * G;
+    cv_end           = cv_end < nvec ? cv_end : nvec;
+    for (int cv0 = cv_beg; cv0 < cv_end; cv0 += G) {
       const int cv      = cv0 + lig;
       const bool col_ok = cv < nvec;
       const DataT* col  = A + grow0 * lda + int64_t(col_ok ? cv : 0) * VEC;
@@ -713,20 +723,28 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
-  // 4. stream the matrix, one warp per unit
+  // 4. stream the matrix, one warp per (unit, part of the columns)
   const int nvec      = int(ncols / p.vec);
   const unsigned g    = next_pow2(unsigned(nvec > 0 ? nvec : 1));
   const int G         = int(g > 32u ? 32u : g);
   const int64_t slots = int64_t(p.n_groups) * p.max_units;
+  const int passes    = (nvec + G - 1) / G;
 #define B2R_LAUNCH_STREAM(VEC_)                                                                              \
   do {                                                                                                       \
     auto kern      = rbk_stream_kernel<DataT, WeightT, SumT, VEC_>;                                          \
     static int occ = resident_ctas(kern, 256, 0);                                                            \
     int64_t ctas   = int64_t(sms) * occ;                                                                     \
-    if (ctas > ceil_div<int64_t>(slots, 8)) ctas = ceil_div<int64_t>(slots, 8);                              \
+    /* about four items per resident warp: cut the columns when the rows alone give fewer */                \
+    const int64_t est_units = ceil_div<int64_t>(nrows, kUnitTarget);                                         \
+    int64_t split           = ceil_div<int64_t>(ctas * 8 * 4, est_units);                                    \
+    if (split > passes) split = passes;                                                                      \
+    while (split > 1 && slots * split >= (int64_t(1) << 30))                                                 \
+      --split;                                                                                               \
+    if (split < 1) split = 1;                                                                                \
+    if (ctas > ceil_div<int64_t>(slots * split, 8)) ctas = ceil_div<int64_t>(slots * split, 8);              \
     kern<<<unsigned(ctas), 256, 0, stream>>>(partial, A, lda, weights, int(ncols), nk, p.window_rows,        \
-                                             p.n_windows, p.group, p.n_groups, p.max_units, G, perm, offs,   \
-                                             uoffs, ukey, ufirst, ulen, counter);                            \
+                                             p.n_windows, p.group, p.n_groups, p.max_units, G, int(split),   \
+                                             perm, offs, uoffs, ukey, ufirst, ulen, counter);                \
   } while (0)
   if (p.vec > 1) {
     B2R_LAUNCH_STREAM(V16);

@@ -24,6 +24,9 @@ pytestmark = pytest.mark.gpu
     (300000, 16, 16384, np.float32, 1e-5),   # one group of 19 windows, about 18 rows per key
     (70000, 32, 24576, np.float32, 1e-5),    # most keys the sorted path takes
     (70000, 32, 30000, np.float32, 1e-5),    # beyond it: shared-memory table slices
+    (40000, 2048, 16, np.float32, 1e-5),     # few long rows: the columns of a work unit are split over warps
+    (40000, 2052, 300, np.float32, 1e-5),    # ... with a ragged last part
+    (33000, 1030, 7, np.float64, 1e-9),
 ])
 @pytest.mark.parametrize("weighted", [False, True])
 @pytest.mark.parametrize("key_dt", [np.int32, np.int64])
@@ -91,9 +94,11 @@ def test_rows_by_key_sorted_pipeline_on_small_inputs(cuda, oracle, knobs, nobs, 
 
 @pytest.mark.parametrize("nobs,cols,nkeys", [(10000, 128, 64), (10000, 128, 4096), (32768, 128, 1), (32768, 36, 70000),
                                              (1, 5, 3), (9999, 1000, 17), (200, 8, 200)])
-def test_rows_by_key_one_launch_kernel(cuda, oracle, nobs, cols, nkeys):
-    """Shapes aimed at the one-launch kernel: the reference's smallest bench shapes
-    (bench/prims/linalg/reduce_rows_by_key.cu:55-72), one key for all rows, far more keys than rows, one row."""
+def test_rows_by_key_one_launch_kernel(cuda, oracle, knobs, nobs, cols, nkeys):
+    """Shapes aimed at the one-launch kernel (forced: by default it only takes inputs of about a megabyte per
+    CTA): the reference's smallest bench shapes (bench/prims/linalg/reduce_rows_by_key.cu:55-72), one key for all
+    rows, far more keys than rows, one row, rows of several column passes."""
+    knobs(B2R_KEY_ALGO="3")
     A, hA = device_synth((nobs, cols), np.float32, 12, "uniform", -1, 1, cuda)
     keys, hk = device_synth((nobs,), np.int32, 13, "int", 0, nkeys, cuda)
     counts = torch.empty(nkeys, dtype=torch.int64, device=cuda)
