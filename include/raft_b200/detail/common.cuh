@@ -89,7 +89,8 @@ B2R_DI VecOf<T, V> load_stream(const T* p)
     memcpy(&r, w, 8);
   } else if constexpr (bytes == 4) {
     uint32_t a;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(a) : "l"(p));
+    // scalar loads of neighbouring lanes and passes share 32-byte sectors: let L1 keep them
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(a) : "l"(p));
     memcpy(&r, &a, 4);
   } else if constexpr (bytes == 2) {
     uint16_t a;

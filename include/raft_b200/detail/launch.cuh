@@ -345,6 +345,9 @@ cudaError_t launch_row_reduce(StoreT* out,
   // lanes per row and chunks per lane: a lane sums up to four chunks of a row by itself (fewer
   // exchanges afterwards), as long as a group still reads at least 64 contiguous bytes per load
   int cpl              = tuning().row_cpl;
+  // scalar path (rows that do not start on 16-byte boundaries): a load brings 4 bytes instead of 16, so
+  // a lane takes four elements of a row whenever the row has them and keeps 32 loads in flight
+  if (cpl == 0 && !vec_ok) cpl = nvec >= 4 ? 4 : (nvec >= 2 ? 2 : 1);
   if (cpl == 0) cpl = nvec >= 32 ? 4 : (nvec >= 8 ? 2 : 1);
   if (cpl != 1 && cpl != 2 && cpl != 4) cpl = 1;
   unsigned g           = next_pow2(unsigned(nvec > 0 ? ceil_div<int>(nvec, cpl) : 1));
@@ -377,8 +380,14 @@ cudaError_t launch_row_reduce(StoreT* out,
       }
     }
   }
-  const int u_rows     = chunks ? 1 : U / cpl;  // rows per group and pass
-  const int64_t per_b  = int64_t(u_rows) * gpw;
+  // rows of 512 elements and more that do not start on 16-byte boundaries: the vector kernel in
+  // chunk mode, one warp per row, takes the few leading / trailing elements of a row one by one
+  // and everything in between with aligned 16-byte loads
+  const bool shifted   = V16 > 1 && !vec_ok && row_len >= 512 && sizeof(InT) * V16 == 16 &&
+                       (reinterpret_cast<uintptr_t>(data) % sizeof(InT)) == 0;
+  const int u_scalar   = cpl == 4 ? 8 : 16;     // rows per group and pass on the scalar path
+  const int u_rows     = (chunks || shifted) ? 1 : (vec_ok ? U / cpl : u_scalar);  // rows per group and pass
+  const int64_t per_b  = int64_t(u_rows) * (shifted ? 1 : gpw);
   const int64_t n_b    = ceil_div<int64_t>(n_rows, per_b);
   const int rl         = int(row_len);
   const int cps_knob   = tuning().row_ctas_per_sm;
@@ -395,9 +404,12 @@ cudaError_t launch_row_reduce(StoreT* out,
     bpc         = ceil_div<int64_t>(bpc, TPB / 32) * (TPB / 32);                                 \
     ctas        = ceil_div<int64_t>(n_b, bpc);                                                   \
     kern<<<unsigned(ctas), TPB, 0, stream>>>(                                                    \
-      out, data, n_rows, rl, ld, init, inplace, main_op, reduce_op, final_op, G, bpc);           \
+      out, data, n_rows, rl, ld, init, inplace, main_op, reduce_op, final_op, shifted ? 32 : G,  \
+      bpc, shifted);                                                                             \
   } while (0)
-  if (vec_ok) {
+  if (shifted) {
+    if constexpr (V16 > 1) { B2R_LAUNCH_ROW(V16, kChunks, U, 1); }
+  } else if (vec_ok) {
     if (chunks) {
       B2R_LAUNCH_ROW(V16, kChunks, U, 1);
     } else if (cpl == 4) {
@@ -411,11 +423,11 @@ cudaError_t launch_row_reduce(StoreT* out,
     if (chunks) {
       B2R_LAUNCH_ROW(1, kChunks, U, 1);
     } else if (cpl == 4) {
-      B2R_LAUNCH_ROW(1, kRows, U / 4, 4);
+      B2R_LAUNCH_ROW(1, kRows, 8, 4);
     } else if (cpl == 2) {
-      B2R_LAUNCH_ROW(1, kRows, U / 2, 2);
+      B2R_LAUNCH_ROW(1, kRows, 16, 2);
     } else {
-      B2R_LAUNCH_ROW(1, kRows, U, 1);
+      B2R_LAUNCH_ROW(1, kRows, 16, 1);
     }
   }
 #undef B2R_LAUNCH_ROW

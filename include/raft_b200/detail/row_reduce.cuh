@@ -82,7 +82,7 @@ template <typename InT,
           int TPB,
           int CPL   = 1,
           typename StoreT = OutT>
-__global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_kernel(StoreT* __restrict__ out,
+__global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 2)) row_reduce_kernel(StoreT* __restrict__ out,
                                                         const InT* __restrict__ data,
                                                         int64_t n_rows,
                                                         int row_len,
@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
                                                         ReduceOp reduce_op,
                                                         FinalOp final_op,
                                                         int G,
-                                                        int64_t batches_per_cta)
+                                                        int64_t batches_per_cta,
+                                                        bool unaligned_rows = false)
 {
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
@@ -206,8 +207,24 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
 #pragma unroll
       for (int u = 0; u < U; ++u)
         init_state<OutT, State, isSum>(st[u], init, lig == 0 && u == 0);
+      // Rows that do not start on a 16-byte boundary (unaligned_rows, vector instantiations only):
+      // up to VEC - 1 leading and trailing elements are taken one by one, by the first lanes of
+      // the group, and the vectors in between are aligned. `head` shifts the column indices.
+      int head = 0, nv = nvec;
+      if constexpr (VEC > 1) {
+        if (unaligned_rows) {
+          const int lead = int(((16u - unsigned(reinterpret_cast<uintptr_t>(rp) & 15u)) & 15u) / sizeof(InT));
+          head           = lead < row_len ? lead : row_len;
+          nv             = (row_len - head) / VEC;
+          const int tail = row_len - head - nv * VEC;
+          if (lig < head) push_element<OutT, IdxT>(st[U - 1], rp[lig], lig, main_op, reduce_op);
+          if (lig < tail)
+            push_element<OutT, IdxT>(st[U - 1], rp[head + nv * VEC + lig], head + nv * VEC + lig, main_op, reduce_op);
+          rp += head;
+        }
+      }
       int c = lig;
-      for (; c + (U - 1) * G < nvec; c += U * G) {
+      for (; c + (U - 1) * G < nv; c += U * G) {
         VecOf<InT, VEC> v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -216,14 +233,23 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 ? 4 : 2)) row_reduce_k
         for (int u = 0; u < U; ++u) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e)
-            push_element<OutT, IdxT>(st[u], v[u].e[e], (c + u * G) * VEC + e, main_op, reduce_op);
+            push_element<OutT, IdxT>(st[u], v[u].e[e], head + (c + u * G) * VEC + e, main_op, reduce_op);
         }
       }
-      for (; c < nvec; c += G) {
-        VecOf<InT, VEC> v = load_stream<InT, VEC>(rp + int64_t(c) * VEC);
+      if (c < nv) {
+        // ragged end of the row: the up to U - 1 chunks that are left go out together, not one by one
+        VecOf<InT, VEC> v[U];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e)
-          push_element<OutT, IdxT>(st[0], v.e[e], c * VEC + e, main_op, reduce_op);
+        for (int u = 0; u < U; ++u)
+          v[u] = load_stream<InT, VEC>(rp + int64_t(c + u * G < nv ? c + u * G : c) * VEC);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (c + u * G < nv) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              push_element<OutT, IdxT>(st[u], v[u].e[e], head + (c + u * G) * VEC + e, main_op, reduce_op);
+          }
+        }
       }
 #pragma unroll
       for (int u = 1; u < U; ++u)
