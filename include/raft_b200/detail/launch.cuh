@@ -123,6 +123,7 @@ struct Tuning {
   int col_tma2d_min_mb     = 256;   // B2R_COL_TMA2D_MB smallest matrix (MiB) for the tiled-TMA kernel of wide matrices
   int tma_stages           = 4;     // B2R_TMA_STAGES stages of the TMA ring (2..8)
   int row_tma              = 0;     // B2R_ROW_TMA    1: TMA-staged tiles for short contiguous rows
+  int row_shifted_min      = 48;    // B2R_ROW_SHIFTED_MIN shortest row off 16-byte boundaries that takes aligned vector loads
   int row_tma_tile_kb      = 16;    // B2R_ROW_TMA_KB tile size of the row kernel's TMA ring, KiB
   int row_tma_stages       = 3;     // B2R_ROW_TMA_STAGES
 };
@@ -155,6 +156,7 @@ inline Tuning read_tuning_from_env()
   if (x.tma_stages < 2) x.tma_stages = 2;
   if (x.tma_stages > 8) x.tma_stages = 8;
   x.row_tma              = env_int("B2R_ROW_TMA", x.row_tma);
+  x.row_shifted_min      = env_int("B2R_ROW_SHIFTED_MIN", x.row_shifted_min);
   x.row_tma_tile_kb      = env_int("B2R_ROW_TMA_KB", x.row_tma_tile_kb);
   x.row_tma_stages       = env_int("B2R_ROW_TMA_STAGES", x.row_tma_stages);
   if (x.row_tma_stages < 2) x.row_tma_stages = 2;
@@ -380,14 +382,19 @@ cudaError_t launch_row_reduce(StoreT* out,
       }
     }
   }
-  // rows of 512 elements and more that do not start on 16-byte boundaries: the vector kernel in
+  // rows of 48 elements and more that do not start on 16-byte boundaries: the vector kernel in
   // chunk mode, one warp per row, takes the few leading / trailing elements of a row one by one
   // and everything in between with aligned 16-byte loads
-  const bool shifted   = V16 > 1 && !vec_ok && row_len >= 512 && sizeof(InT) * V16 == 16 &&
+  const bool shifted   = V16 > 1 && !vec_ok && row_len >= tuning().row_shifted_min && sizeof(InT) * V16 == 16 &&
                        (reinterpret_cast<uintptr_t>(data) % sizeof(InT)) == 0;
+  // lanes per row in that mode: about sixteen vectors per lane (measured best: few lanes per row keep
+  // the per-row reduction short), at least four lanes (they also take the up to three leading and
+  // trailing elements)
+  unsigned gs          = next_pow2(unsigned(ceil_div<int64_t>(row_len / (V16 > 1 ? V16 : 1), 16)));
+  const int G_shifted  = int(gs > 32u ? 32u : (gs < 4u ? 4u : gs));
   const int u_scalar   = cpl == 4 ? 8 : 16;     // rows per group and pass on the scalar path
   const int u_rows     = (chunks || shifted) ? 1 : (vec_ok ? U / cpl : u_scalar);  // rows per group and pass
-  const int64_t per_b  = int64_t(u_rows) * (shifted ? 1 : gpw);
+  const int64_t per_b  = int64_t(u_rows) * (shifted ? 32 / G_shifted : gpw);
   const int64_t n_b    = ceil_div<int64_t>(n_rows, per_b);
   const int rl         = int(row_len);
   const int cps_knob   = tuning().row_ctas_per_sm;
@@ -404,7 +411,8 @@ cudaError_t launch_row_reduce(StoreT* out,
     bpc         = ceil_div<int64_t>(bpc, TPB / 32) * (TPB / 32);                                 \
     ctas        = ceil_div<int64_t>(n_b, bpc);                                                   \
     kern<<<unsigned(ctas), TPB, 0, stream>>>(                                                    \
-      out, data, n_rows, rl, ld, init, inplace, main_op, reduce_op, final_op, shifted ? 32 : G,  \
+      out, data, n_rows, rl, ld, init, inplace, main_op, reduce_op, final_op,                    \
+      shifted ? G_shifted : G,                                                                   \
       bpc, shifted);                                                                             \
   } while (0)
   if (shifted) {
