@@ -13,6 +13,7 @@
 #include "col_reduce_tma.cuh"
 #include "col_reduce_tma2d.cuh"
 #include "row_reduce.cuh"
+#include "row_reduce_staged.cuh"
 #include "row_reduce_tma.cuh"
 
 #include <atomic>
@@ -126,6 +127,12 @@ struct Tuning {
   int row_shifted_min      = 48;    // B2R_ROW_SHIFTED_MIN shortest row off 16-byte boundaries that takes aligned vector loads
   int row_tma_tile_kb      = 16;    // B2R_ROW_TMA_KB tile size of the row kernel's TMA ring, KiB
   int row_tma_stages       = 3;     // B2R_ROW_TMA_STAGES
+  int row_staged           = 1;     // B2R_ROW_STAGED  1: shared-memory staging for contiguous rows off 16-byte boundaries, 2: off
+  int row_staged_max       = 1024;   // B2R_ROW_STAGED_MAX longest such row (elements) that is staged
+  int row_staged_min_kb    = 8192;  // B2R_ROW_STAGED_MIN_KB smallest matrix (KiB) that is staged, rows up to 64 elements
+  int row_staged_wide_min_kb = 131072;  // B2R_ROW_STAGED_WIDE_MIN_KB the same for longer rows (the direct kernels ramp up faster)
+  int row_staged_tile_kb   = 48;    // B2R_ROW_STAGED_KB tile size of that ring, KiB
+  int row_staged_ring_kb   = 100;   // B2R_ROW_STAGED_RING_KB shared memory of one CTA's ring, KiB (100: two CTAs per SM)
 };
 
 inline int env_int(const char* name, int dflt)
@@ -161,6 +168,13 @@ inline Tuning read_tuning_from_env()
   x.row_tma_stages       = env_int("B2R_ROW_TMA_STAGES", x.row_tma_stages);
   if (x.row_tma_stages < 2) x.row_tma_stages = 2;
   if (x.row_tma_stages > 8) x.row_tma_stages = 8;
+  x.row_staged           = env_int("B2R_ROW_STAGED", x.row_staged);
+  x.row_staged_max       = env_int("B2R_ROW_STAGED_MAX", x.row_staged_max);
+  x.row_staged_min_kb    = env_int("B2R_ROW_STAGED_MIN_KB", x.row_staged_min_kb);
+  x.row_staged_wide_min_kb = env_int("B2R_ROW_STAGED_WIDE_MIN_KB", x.row_staged_wide_min_kb);
+  x.row_staged_tile_kb   = env_int("B2R_ROW_STAGED_KB", x.row_staged_tile_kb);
+  x.row_staged_ring_kb   = env_int("B2R_ROW_STAGED_RING_KB", x.row_staged_ring_kb);
+  if (x.row_staged_ring_kb > 200) x.row_staged_ring_kb = 200;
   return x;
 }
 
@@ -379,6 +393,55 @@ cudaError_t launch_row_reduce(StoreT* out,
                                                            reduce_op, final_op, G, int(tile_rows), rpc, stages,
                                                            nullptr);
         return cudaGetLastError();
+      }
+    }
+  }
+  // contiguous rows that do not start on 16-byte boundaries: blocks of rows do, so whole blocks are
+  // copied into shared memory (cp.async.bulk) and summed from there, where alignment costs nothing
+  if constexpr (V16 > 1 && sizeof(InT) >= 2) {
+    const size_t row_bytes = size_t(row_len) * sizeof(InT);
+    if (tuning().row_staged == 1 && !vec_ok && ld == row_len && aligned16(data) &&
+        row_len <= tuning().row_staged_max &&
+        size_t(n_rows) * row_bytes >=
+          (size_t(row_len <= 64 ? tuning().row_staged_min_kb : tuning().row_staged_wide_min_kb) << 10)) {
+      // every m-th row starts on a boundary
+      size_t gcd16 = 16;
+      while (row_bytes % gcd16 != 0) gcd16 >>= 1;
+      const int m           = int(16 / gcd16);
+      const size_t budget   = size_t(tuning().row_staged_tile_kb) << 10;
+      int Gs                = 1;
+      while (Gs < 32 && size_t(kTmaConsumers / Gs) * row_bytes > budget) Gs <<= 1;
+      const int rpp         = kTmaConsumers / Gs;  // rows per pass of a CTA, a multiple of 8 >= m
+      const int64_t n_main  = n_rows - n_rows % m;
+      const size_t ring     = size_t(tuning().row_staged_ring_kb) << 10;
+      auto kern             = row_reduce_staged_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, StoreT>;
+      if (size_t(rpp) * row_bytes <= budget && 2 * (budget + 128) <= ring && rpp % m == 0 && n_main > 0) {
+        int64_t k = int64_t(budget / (size_t(rpp) * row_bytes));
+        // CTAs resident per SM: two with a ring of up to 100 KB, else one
+        const int64_t ctas0 = int64_t(sm_count()) * (ring <= (size_t(104) << 10) ? 2 : 1);
+        // small inputs: smaller tiles, so that every CTA still gets a few of them
+        const int64_t k_fit = n_main / (int64_t(rpp) * ctas0 * 4);
+        if (k > k_fit) k = k_fit < 1 ? 1 : k_fit;
+        const int64_t tile_rows = int64_t(rpp) * k;
+        const size_t stage      = (size_t(tile_rows) * row_bytes + 127) / 128 * 128;
+        // what keeps HBM busy is the bytes in flight: as many stages as the ring holds
+        int stages              = int(ring / stage);
+        stages                  = stages > kTmaMaxStages ? kTmaMaxStages : stages;
+        const size_t smem       = size_t(stages) * stage;
+        cudaError_t ea          = ensure_dynamic_smem(kern, smem);
+        if (ea != cudaSuccess) return ea;
+        int64_t rpc             = ceil_div<int64_t>(n_main, ctas0);
+        rpc                     = ceil_div<int64_t>(rpc, tile_rows) * tile_rows;
+        const int64_t ctas      = ceil_div<int64_t>(n_main, rpc);
+        kern<<<unsigned(ctas), kTmaThreads, smem, stream>>>(out, data, n_main, int(row_len), init, inplace, main_op,
+                                                           reduce_op, final_op, Gs, int(tile_rows), rpc, stages,
+                                                           nullptr);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess || n_main == n_rows) return e;
+        // the up to m - 1 rows behind the last boundary: the direct kernels
+        return launch_row_reduce<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, StoreT>(
+          out + n_main, data + n_main * row_len, n_rows - n_main, row_len, ld, init, inplace, main_op, reduce_op,
+          final_op, stream, ws);
       }
     }
   }

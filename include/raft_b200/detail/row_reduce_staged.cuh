@@ -1,0 +1,195 @@
+// Row reduction of contiguous rows that do NOT start on 16-byte boundaries (odd widths), staged
+// through shared memory.
+//
+// A global load can only be as wide as the alignment of a row, so a kernel that reads such rows
+// directly is left with 4-byte loads. Whole blocks of rows, however, are 16-byte aligned: with
+// m = 16 / gcd(16, row bytes), every m-th row starts on a boundary, and a block of a multiple of m
+// rows is a multiple of 16 bytes long. One producer thread copies such blocks into a ring of
+// shared-memory stages with cp.async.bulk (no register, no alignment concern per row), and the
+// consumers read single elements out of shared memory, where alignment costs nothing: G lanes per
+// row (G = 1 for rows up to 32 elements: a lane sums its row alone, no shuffle at all), lanes of a
+// warp on consecutive rows, so that for an odd row length all 32 lanes hit different banks.
+// The results of a warp are consecutive rows: one coalesced store.
+//
+// Every mbarrier wait is bounded (see col_reduce_tma.cuh); a CTA whose wait runs out stops, drains
+// its copies in flight and writes NaN to the floating-point outputs it did not finish.
+#pragma once
+
+#include "col_reduce_tma.cuh"
+#include "row_reduce.cuh"
+
+namespace raft_b200 {
+namespace detail {
+
+constexpr int kStagedShortRow = 8;  // rows up to this many elements: four rows per lane at a time
+
+template <typename InT, typename OutT, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp,
+          typename StoreT = OutT>
+__global__ void __launch_bounds__(kTmaThreads, 2) row_reduce_staged_kernel(StoreT* __restrict__ out,
+                                                                          const InT* __restrict__ data,
+                                                                          int64_t n_rows,
+                                                                          int row_len,
+                                                                          OutT init,
+                                                                          bool inplace,
+                                                                          MainOp main_op,
+                                                                          ReduceOp reduce_op,
+                                                                          FinalOp final_op,
+                                                                          int G,
+                                                                          int tile_rows,
+                                                                          int64_t rows_per_cta,
+                                                                          int STAGES,
+                                                                          int* __restrict__ status)
+{
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  extern __shared__ __align__(128) unsigned char smem_tma[];
+  __shared__ __align__(8) uint64_t s_full[kTmaMaxStages];
+  __shared__ __align__(8) uint64_t s_empty[kTmaMaxStages];
+  __shared__ int s_abort;
+
+  const size_t row_bytes    = size_t(row_len) * sizeof(InT);
+  const size_t stage_stride = (size_t(tile_rows) * row_bytes + 127) / 128 * 128;
+  const int tid             = threadIdx.x;
+  const bool producer       = tid >= kTmaConsumers;
+  const int64_t r_beg       = int64_t(blockIdx.x) * rows_per_cta;
+  int64_t r_end             = r_beg + rows_per_cta;
+  r_end                     = r_end < n_rows ? r_end : n_rows;
+  const int64_t rows        = r_end > r_beg ? r_end - r_beg : 0;
+  const int n_tiles         = int((rows + tile_rows - 1) / tile_rows);
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], kTmaConsumers / 32);
+    }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  volatile int* abort_flag = &s_abort;
+
+  if (producer) {
+    if (tid == kTmaConsumers) {
+      int issued = 0;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s          = t % STAGES;
+        const unsigned phase = (t / STAGES) & 1u;
+        if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag)) break;
+        const int64_t row0 = r_beg + int64_t(t) * tile_rows;
+        const int64_t nr   = (r_end - row0) < tile_rows ? (r_end - row0) : tile_rows;
+        // the host makes n_rows * row_bytes, tile_rows * row_bytes and rows_per_cta * row_bytes
+        // multiples of 16, so every copy starts on a boundary and has a legal size
+        const unsigned nb  = unsigned(size_t(nr) * row_bytes);
+        mbar_expect_tx(&s_full[s], nb);
+        bulk_load(smem_tma + s * stage_stride, reinterpret_cast<const unsigned char*>(data) + size_t(row0) * row_bytes,
+                  nb, &s_full[s]);
+        issued = t + 1;
+      }
+      if (*abort_flag != 0) {
+        const int first = issued > STAGES ? issued - STAGES : 0;
+        for (int t = first; t < issued; ++t) {
+          unsigned spin = 0;
+          while (!mbar_try_wait(&s_full[t % STAGES], (t / STAGES) & 1u) && ++spin < kSpinLimit) {}
+        }
+        if (status != nullptr) atomicExch(status, 1);
+      }
+    }
+    return;
+  }
+
+  const int lane = tid & 31;
+  const int lg   = 31 - __clz(G);
+  const int lig  = tid & (G - 1);  // lane within the group of a row
+  const int slot = tid >> lg;      // row slot of this thread within a pass
+  const int rpp  = kTmaConsumers >> lg;  // rows per pass of the CTA
+
+  int t = 0;
+  for (; t < n_tiles; ++t) {
+    const int s          = t % STAGES;
+    const unsigned phase = (t / STAGES) & 1u;
+    if (!mbar_wait_bounded(&s_full[s], phase, abort_flag)) break;
+    const int64_t tile_row0 = r_beg + int64_t(t) * tile_rows;
+    const int nr            = int((r_end - tile_row0) < tile_rows ? (r_end - tile_row0) : tile_rows);
+    const InT* tile         = reinterpret_cast<const InT*>(smem_tma + s * stage_stride);
+    if (G == 1 && row_len <= kStagedShortRow) {
+      // very short rows: a lane works on four rows at a time, so that their dependent chains overlap
+      constexpr int R = 4;
+      for (int lr0 = 0; lr0 < nr; lr0 += R * kTmaConsumers) {
+        State st[R];
+        const InT* row[R];
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
+          const int lr = lr0 + u * kTmaConsumers + tid;
+          row[u]       = tile + size_t(lr < nr ? lr : nr - 1) * row_len;
+          init_state<OutT, State, isSum>(st[u], init, true);
+        }
+        for (int c = 0; c < row_len; ++c) {
+          InT v[R];
+#pragma unroll
+          for (int u = 0; u < R; ++u)
+            v[u] = row[u][c];
+#pragma unroll
+          for (int u = 0; u < R; ++u)
+            push_element<OutT, IdxT>(st[u], v[u], c, main_op, reduce_op);
+        }
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
+          const int lr = lr0 + u * kTmaConsumers + tid;
+          if (lr < nr) {
+            const int64_t r = tile_row0 + lr;
+            OutT v          = st[u].value();
+            if constexpr (std::is_same<StoreT, OutT>::value) {
+              if (inplace) v = reduce_op(out[r], v);
+            }
+            out[r] = final_op(v);
+          }
+        }
+      }
+    } else {
+      // whole warps walk the passes together (the shuffles below need all lanes)
+      for (int lr0 = 0; lr0 < nr; lr0 += rpp) {
+        const int lr   = lr0 + slot;
+        const bool ok  = lr < nr;
+        const InT* row = tile + size_t(ok ? lr : nr - 1) * row_len;
+        State st;
+        init_state<OutT, State, isSum>(st, init, lig == 0);
+        int c = lig;
+        for (; c + 3 * G < row_len; c += 4 * G) {
+          InT v[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            v[k] = row[c + k * G];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            push_element<OutT, IdxT>(st, v[k], c + k * G, main_op, reduce_op);
+        }
+        for (; c < row_len; c += G)
+          push_element<OutT, IdxT>(st, row[c], c, main_op, reduce_op);
+        for (int off = G >> 1; off > 0; off >>= 1) {
+          State got = shfl_xor_any(st, off);
+          st.merge(got, reduce_op);
+        }
+        if (ok && lig == 0) {
+          const int64_t r = tile_row0 + lr;
+          OutT v          = st.value();
+          if constexpr (std::is_same<StoreT, OutT>::value) {
+            if (inplace) v = reduce_op(out[r], v);
+          }
+          out[r] = final_op(v);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&s_empty[s]);
+  }
+  if (t < n_tiles) {
+    // a bounded wait ran out: make it visible - the rows this CTA did not finish become NaN
+    if constexpr (std::is_floating_point<StoreT>::value) {
+      for (int64_t r = r_beg + int64_t(t) * tile_rows + tid; r < r_end; r += kTmaConsumers)
+        out[r] = StoreT(NAN);
+    }
+  }
+}
+
+}  // namespace detail
+}  // namespace raft_b200

@@ -298,6 +298,58 @@ def test_rows_tma_staged(cuda, oracle, knobs, rows, cols):
     oracle.assert_approx(linalg.reduce(tu, linalg.ALONG_ROWS).cpu().numpy(), got.cpu().numpy(), 1e-6)
 
 
+@pytest.mark.parametrize("rows,cols,dt", [(100003, 1, np.float32), (70001, 2, np.float32), (50002, 3, np.float32),
+                                          (33333, 7, np.float32), (40001, 8 + 1, np.float32), (20001, 17, np.float32),
+                                          (9999, 33, np.float32), (12346, 65, np.float32), (5003, 129, np.float32),
+                                          (3001, 513, np.float32), (2002, 1001, np.float32), (1003, 1023, np.float32),
+                                          (20001, 7, np.float64), (5001, 131, np.float64), (30003, 13, np.float16),
+                                          (25001, 9, np.int32)])
+@pytest.mark.parametrize("tile_kb", [None, "6"])
+def test_rows_staged_odd_widths(cuda, oracle, knobs, rows, cols, dt, tile_kb):
+    """Contiguous rows off 16-byte boundaries through the shared-memory staged kernel, forced onto small inputs:
+    lane-per-row, four rows per lane, 2..32 lanes per row; row counts that leave rows behind the last 16-byte
+    boundary; default and tiny tiles (many tiles per CTA, every ring depth)."""
+    if tile_kb is not None and cols * np.dtype(dt).itemsize * 8 > 6 * 1024:
+        pytest.skip("eight rows do not fit the tiny tile")
+    knobs(B2R_ROW_STAGED_MIN_KB="0", B2R_ROW_STAGED_WIDE_MIN_KB="0", B2R_ROW_STAGED_KB=tile_kb)
+    t, host = device_synth((rows, cols), dt, 29, "uniform" if dt == np.float16 else "int", -4, 5, cuda)
+    out_dt = torch.float32 if dt == np.float16 else None
+    got = linalg.reduce(t, linalg.ALONG_ROWS, out_dtype=out_dt)
+    if dt == np.float16:
+        oracle.assert_approx(oracle.reduce(host), got.cpu().numpy(), 1e-5)
+        return
+    assert np.array_equal(got.cpu().numpy().astype(np.float64), host.astype(np.float64).sum(1))
+    if dt == np.int32:
+        return
+    got = linalg.norm(t, "L2", linalg.ALONG_ROWS, fin_op="sqrt")
+    oracle.assert_approx(oracle.reduce(host, main_op="sq", final_op="sqrt"), got.cpu().numpy(), 1e-6)
+    kv = linalg.reduce(t, linalg.ALONG_ROWS, main_op="to_kvp", reduce_op="argmin", init=float("inf"))
+    ek, ev = oracle.reduce(host, main_op="to_kvp", reduce_op="argmin", init=np.inf)
+    assert np.array_equal(kv.keys.cpu().numpy().astype(np.int64), ek)
+    assert np.array_equal(kv.values.cpu().numpy().astype(np.float64), ev)
+    if dt == np.float32:
+        idx = torch.empty(rows, dtype=torch.int32, device=cuda)
+        linalg.argmin(t, idx)
+        assert np.array_equal(idx.cpu().numpy().astype(np.int64), ek)
+    prev = got.clone()
+    linalg.reduce(t, linalg.ALONG_ROWS, got, inplace=True, main_op="abs", reduce_op="max")
+    assert np.array_equal(got.cpu().numpy(), np.maximum(prev.cpu().numpy(), np.abs(host).max(1)))
+    # same bits as the direct kernels for a sum of uniform data (both carry fp32 sums in fp64)
+    tu, hu = device_synth((rows, cols), dt, 30, "uniform", -1, 1, cuda)
+    staged = linalg.reduce(tu, linalg.ALONG_ROWS, init=0.5)
+    knobs(B2R_ROW_STAGED="2")
+    direct = linalg.reduce(tu, linalg.ALONG_ROWS, init=0.5)
+    oracle.assert_approx(oracle.reduce(hu, init=0.5), staged.cpu().numpy(), 1e-5 if dt == np.float32 else 1e-12)
+    oracle.assert_approx(direct.cpu().numpy(), staged.cpu().numpy(), 1e-6 if dt == np.float32 else 1e-13)
+
+
+def test_rows_staged_full_size(cuda):
+    """40 000 003 x 7 fp32 (1.1 GB, default policy, three rows behind the last boundary): exact integer sums."""
+    t, host = device_synth((40000003, 7), np.float32, 33, "int", 0, 16, cuda)
+    got = linalg.reduce(t, linalg.ALONG_ROWS)
+    assert np.array_equal(got.cpu().numpy().astype(np.int64), host.sum(axis=1, dtype=np.int64))
+
+
 @pytest.mark.parametrize("rows,cols", [(0, 5), (5, 0), (1, 1), (1, 300), (300, 1), (2, 2)])
 def test_degenerate_shapes(cuda, oracle, rows, cols):
     t = torch.full((rows, cols), 2.0, dtype=torch.float32, device=cuda)
