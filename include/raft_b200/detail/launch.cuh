@@ -128,6 +128,8 @@ struct Tuning {
   int row_tma_tile_kb      = 16;    // B2R_ROW_TMA_KB tile size of the row kernel's TMA ring, KiB
   int row_tma_stages       = 3;     // B2R_ROW_TMA_STAGES
   int row_staged           = 1;     // B2R_ROW_STAGED  1: shared-memory staging for contiguous rows off 16-byte boundaries, 2: off
+  int row_staged_aligned   = 1;     // B2R_ROW_STAGED_ALIGNED aligned rows staged 1: when the direct kernel would leave a tenth of its load slots empty, 2: always, 3: never
+  int row_staged_aligned_max = 800;  // B2R_ROW_STAGED_ALIGNED_MAX longest aligned row (elements) staged by rule 1
   int row_staged_max       = 1024;   // B2R_ROW_STAGED_MAX longest such row (elements) that is staged
   int row_staged_min_kb    = 8192;  // B2R_ROW_STAGED_MIN_KB smallest matrix (KiB) that is staged, rows up to 64 elements
   int row_staged_wide_min_kb = 131072;  // B2R_ROW_STAGED_WIDE_MIN_KB the same for longer rows (the direct kernels ramp up faster)
@@ -169,6 +171,8 @@ inline Tuning read_tuning_from_env()
   if (x.row_tma_stages < 2) x.row_tma_stages = 2;
   if (x.row_tma_stages > 8) x.row_tma_stages = 8;
   x.row_staged           = env_int("B2R_ROW_STAGED", x.row_staged);
+  x.row_staged_aligned   = env_int("B2R_ROW_STAGED_ALIGNED", x.row_staged_aligned);
+  x.row_staged_aligned_max = env_int("B2R_ROW_STAGED_ALIGNED_MAX", x.row_staged_aligned_max);
   x.row_staged_max       = env_int("B2R_ROW_STAGED_MAX", x.row_staged_max);
   x.row_staged_min_kb    = env_int("B2R_ROW_STAGED_MIN_KB", x.row_staged_min_kb);
   x.row_staged_wide_min_kb = env_int("B2R_ROW_STAGED_WIDE_MIN_KB", x.row_staged_wide_min_kb);
@@ -396,46 +400,94 @@ cudaError_t launch_row_reduce(StoreT* out,
       }
     }
   }
-  // contiguous rows that do not start on 16-byte boundaries: blocks of rows do, so whole blocks are
-  // copied into shared memory (cp.async.bulk) and summed from there, where alignment costs nothing
+  // Rows staged through shared memory (row_reduce_staged.cuh), contiguous matrices only:
+  //  - rows that do not start on 16-byte boundaries: blocks of rows do, so whole blocks are copied
+  //    (cp.async.bulk) and summed from shared memory, where alignment costs nothing;
+  //  - aligned rows whose vector count fits the power-of-two lane groups of the direct kernels badly.
   if constexpr (V16 > 1 && sizeof(InT) >= 2) {
     const size_t row_bytes = size_t(row_len) * sizeof(InT);
-    if (tuning().row_staged == 1 && !vec_ok && ld == row_len && aligned16(data) &&
-        row_len <= tuning().row_staged_max &&
-        size_t(n_rows) * row_bytes >=
-          (size_t(row_len <= 64 ? tuning().row_staged_min_kb : tuning().row_staged_wide_min_kb) << 10)) {
+    bool staged            = tuning().row_staged == 1 && ld == row_len && aligned16(data) &&
+                  row_len <= tuning().row_staged_max &&
+                  size_t(n_rows) * row_bytes >=
+                    (size_t(row_len <= 64 ? tuning().row_staged_min_kb : tuning().row_staged_wide_min_kb) << 10);
+    if (staged && vec_ok) {
+      // slots of the direct kernel's lane groups that would stay empty
+      const int64_t slots = int64_t(G) * cpl * ceil_div<int64_t>(nvec, int64_t(G) * cpl);
+      const int mode      = tuning().row_staged_aligned;  // 1: when a tenth of the slots is wasted, 2: always, 3: never
+      // (rows of up to 64 bytes: the staged kernel's lane per row beats the direct kernel's shuffles)
+      staged              = mode == 2 || (mode == 1 && (int64_t(nvec) * 10 < slots * 9 || row_bytes <= 64) &&
+                                 row_len <= tuning().row_staged_aligned_max);
+    }
+    if (staged) {
       // every m-th row starts on a boundary
       size_t gcd16 = 16;
       while (row_bytes % gcd16 != 0) gcd16 >>= 1;
       const int m           = int(16 / gcd16);
       const size_t budget   = size_t(tuning().row_staged_tile_kb) << 10;
-      int Gs                = 1;
-      while (Gs < 32 && size_t(kTmaConsumers / Gs) * row_bytes > budget) Gs <<= 1;
-      const int rpp         = kTmaConsumers / Gs;  // rows per pass of a CTA, a multiple of 8 >= m
       const int64_t n_main  = n_rows - n_rows % m;
       const size_t ring     = size_t(tuning().row_staged_ring_kb) << 10;
-      auto kern             = row_reduce_staged_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, StoreT>;
-      if (size_t(rpp) * row_bytes <= budget && 2 * (budget + 128) <= ring && rpp % m == 0 && n_main > 0) {
-        int64_t k = int64_t(budget / (size_t(rpp) * row_bytes));
-        // CTAs resident per SM: two with a ring of up to 100 KB, else one
-        const int64_t ctas0 = int64_t(sm_count()) * (ring <= (size_t(104) << 10) ? 2 : 1);
-        // small inputs: smaller tiles, so that every CTA still gets a few of them
-        const int64_t k_fit = n_main / (int64_t(rpp) * ctas0 * 4);
-        if (k > k_fit) k = k_fit < 1 ? 1 : k_fit;
-        const int64_t tile_rows = int64_t(rpp) * k;
-        const size_t stage      = (size_t(tile_rows) * row_bytes + 127) / 128 * 128;
+      // rows a tile may hold: the budget, less for small inputs so that every CTA still gets a few tiles
+      // (two CTAs resident per SM with a ring of up to 100 KB, else one)
+      const int64_t ctas0 = int64_t(sm_count()) * (ring <= (size_t(104) << 10) ? 2 : 1);
+      int64_t max_rows    = int64_t(budget / row_bytes);
+      const int64_t fit   = n_main / (ctas0 * 4);
+      if (max_rows > fit) max_rows = fit;
+      max_rows            = max_rows / m * m;
+      if (max_rows < m) max_rows = m;
+      if (size_t(max_rows) * row_bytes <= budget && 2 * (budget + 128) <= ring && n_main > 0) {
+        // Lanes per row Gs and rows per tile: a tile is a whole number of passes of the 256 consumers
+        // (256 / Gs rows each). What a lane does per row besides summing - set-up, shuffles, the store -
+        // weighs more the fewer vectors it gets, so: the FEWEST lanes per row whose tiles still fill
+        // seven tenths of the ring (the bytes in flight), else the choice that fills it best.
+        // A last pass that is at least nine tenths busy counts as whole.
+        int Gs            = 32;
+        int64_t tile_rows = max_rows;  // rows too long for a whole pass: one partial pass with 32 lanes per row
+        size_t best_fill  = 0;
+        for (int g2 = 1; g2 <= 32; g2 <<= 1) {
+          const int64_t rpp = kTmaConsumers / g2;
+          int64_t tr        = max_rows / rpp * rpp;  // rpp is a multiple of 8, so of m
+          if (max_rows * 10 >= ceil_div<int64_t>(max_rows, rpp) * rpp * 9) tr = max_rows;
+          if (tr == 0 || (g2 > 1 && nvec < 2 * g2)) continue;
+          const size_t tile = (size_t(tr) * row_bytes + 127) / 128 * 128;
+          size_t n_st       = ring / tile;
+          n_st              = n_st > size_t(kTmaMaxStages) ? size_t(kTmaMaxStages) : n_st;
+          const size_t fill = n_st * tile;
+          if (fill > best_fill) {
+            best_fill = fill;
+            Gs        = g2;
+            tile_rows = tr;
+          }
+          if (fill * 10 >= ring * 7) break;
+        }
+        // Bank rotation, 16-byte loads only: eight lanes are served at a time, so with fewer than eight
+        // lanes per row they sit on different rows, (row pitch + rot) vectors apart; with that distance
+        // congruent to Gs modulo 2 Gs they fall into different banks. Single elements of rows off the
+        // boundaries: the pitch is odd or twice an odd number, at worst a two-way conflict - not worth
+        // the index arithmetic per element.
+        const int rot       = (vec_ok && Gs < 8) ? (Gs - nvec % (2 * Gs) + 2 * Gs) % (2 * Gs) : 0;
+        const size_t stage  = (size_t(tile_rows) * row_bytes + 127) / 128 * 128;
         // what keeps HBM busy is the bytes in flight: as many stages as the ring holds
-        int stages              = int(ring / stage);
-        stages                  = stages > kTmaMaxStages ? kTmaMaxStages : stages;
-        const size_t smem       = size_t(stages) * stage;
-        cudaError_t ea          = ensure_dynamic_smem(kern, smem);
-        if (ea != cudaSuccess) return ea;
+        int stages          = int(ring / stage);
+        stages              = stages > kTmaMaxStages ? kTmaMaxStages : stages;
+        const size_t smem   = size_t(stages) * stage;
         int64_t rpc             = ceil_div<int64_t>(n_main, ctas0);
         rpc                     = ceil_div<int64_t>(rpc, tile_rows) * tile_rows;
         const int64_t ctas      = ceil_div<int64_t>(n_main, rpc);
-        kern<<<unsigned(ctas), kTmaThreads, smem, stream>>>(out, data, n_main, int(row_len), init, inplace, main_op,
-                                                           reduce_op, final_op, Gs, int(tile_rows), rpc, stages,
-                                                           nullptr);
+#define B2R_LAUNCH_STAGED(VEC_)                                                                              \
+  do {                                                                                                       \
+    auto kern      = row_reduce_staged_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, StoreT>;     \
+    cudaError_t ea = ensure_dynamic_smem(kern, smem);                                                        \
+    if (ea != cudaSuccess) return ea;                                                                        \
+    kern<<<unsigned(ctas), kTmaThreads, smem, stream>>>(out, data, n_main, int(row_len), init, inplace,      \
+                                                       main_op, reduce_op, final_op, Gs, rot, int(tile_rows), \
+                                                       rpc, stages, nullptr);                                \
+  } while (0)
+        if (vec_ok) {
+          B2R_LAUNCH_STAGED(V16);
+        } else {
+          B2R_LAUNCH_STAGED(1);
+        }
+#undef B2R_LAUNCH_STAGED
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess || n_main == n_rows) return e;
         // the up to m - 1 rows behind the last boundary: the direct kernels

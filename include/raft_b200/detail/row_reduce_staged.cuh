@@ -11,6 +11,14 @@
 // warp on consecutive rows, so that for an odd row length all 32 lanes hit different banks.
 // The results of a warp are consecutive rows: one coalesced store.
 //
+// Rows that DO start on 16-byte boundaries take the same route with 16-byte shared-memory loads
+// (VEC elements each) when their length fits the direct kernels badly (lane groups are powers of
+// two there; a row of, say, 24 or 100 vectors leaves a quarter of the load slots empty). Where the
+// row pitch would put the lanes of a warp into the same banks, every row slot starts a little
+// further into its row and wraps around (`rot` vectors per slot, chosen by the host): a reduction
+// does not care in which order the elements of a row arrive, and main_op still gets each element's
+// true column.
+//
 // Every mbarrier wait is bounded (see col_reduce_tma.cuh); a CTA whose wait runs out stops, drains
 // its copies in flight and writes NaN to the floating-point outputs it did not finish.
 #pragma once
@@ -23,7 +31,7 @@ namespace detail {
 
 constexpr int kStagedShortRow = 8;  // rows up to this many elements: four rows per lane at a time
 
-template <typename InT, typename OutT, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp,
+template <typename InT, typename OutT, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp, int VEC,
           typename StoreT = OutT>
 __global__ void __launch_bounds__(kTmaThreads, 2) row_reduce_staged_kernel(StoreT* __restrict__ out,
                                                                           const InT* __restrict__ data,
@@ -35,6 +43,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_reduce_staged_kernel(Store
                                                                           ReduceOp reduce_op,
                                                                           FinalOp final_op,
                                                                           int G,
+                                                                          int rot,
                                                                           int tile_rows,
                                                                           int64_t rows_per_cta,
                                                                           int STAGES,
@@ -97,11 +106,18 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_reduce_staged_kernel(Store
     return;
   }
 
+  using Vec      = VecOf<InT, VEC>;
   const int lane = tid & 31;
   const int lg   = 31 - __clz(G);
   const int lig  = tid & (G - 1);  // lane within the group of a row
   const int slot = tid >> lg;      // row slot of this thread within a pass
   const int rpp  = kTmaConsumers >> lg;  // rows per pass of the CTA
+  const int nvec = row_len / VEC;        // VEC divides row_len (VEC = 1 for rows off 16-byte boundaries)
+  // every row slot starts `rot` vectors further into its row (and wraps): the host picks rot so that the
+  // lanes of a warp, which sit on different rows, fall into different shared-memory banks
+  const int shift = rot == 0 ? 0 : int((unsigned(slot) * unsigned(rot)) % unsigned(nvec));
+  const int n_full = nvec >> lg;       // vectors that every lane of a group takes
+  const int n_rem  = nvec & (G - 1);   // lanes of a group that take one more
 
   int t = 0;
   for (; t < n_tiles; ++t) {
@@ -110,27 +126,32 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_reduce_staged_kernel(Store
     if (!mbar_wait_bounded(&s_full[s], phase, abort_flag)) break;
     const int64_t tile_row0 = r_beg + int64_t(t) * tile_rows;
     const int nr            = int((r_end - tile_row0) < tile_rows ? (r_end - tile_row0) : tile_rows);
-    const InT* tile         = reinterpret_cast<const InT*>(smem_tma + s * stage_stride);
-    if (G == 1 && row_len <= kStagedShortRow) {
+    const Vec* tile         = reinterpret_cast<const Vec*>(smem_tma + s * stage_stride);
+    int lr_begin = 0;  // rows of the tile already done by the four-rows-per-lane loop
+    if (G == 1 && nvec <= kStagedShortRow && (rot == 0 || (nvec & 3) != 0)) {  // at worst a two-way bank conflict
       // very short rows: a lane works on four rows at a time, so that their dependent chains overlap
       constexpr int R = 4;
-      for (int lr0 = 0; lr0 < nr; lr0 += R * kTmaConsumers) {
+      for (; lr_begin + R * kTmaConsumers <= nr; lr_begin += R * kTmaConsumers) {
+        const int lr0 = lr_begin;
         State st[R];
-        const InT* row[R];
+        const Vec* row[R];
 #pragma unroll
         for (int u = 0; u < R; ++u) {
           const int lr = lr0 + u * kTmaConsumers + tid;
-          row[u]       = tile + size_t(lr < nr ? lr : nr - 1) * row_len;
+          row[u]       = tile + size_t(lr < nr ? lr : nr - 1) * nvec;
           init_state<OutT, State, isSum>(st[u], init, true);
         }
-        for (int c = 0; c < row_len; ++c) {
-          InT v[R];
+        for (int c = 0; c < nvec; ++c) {
+          Vec v[R];
 #pragma unroll
           for (int u = 0; u < R; ++u)
             v[u] = row[u][c];
 #pragma unroll
-          for (int u = 0; u < R; ++u)
-            push_element<OutT, IdxT>(st[u], v[u], c, main_op, reduce_op);
+          for (int u = 0; u < R; ++u) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              push_element<OutT, IdxT>(st[u], v[u].e[e], c * VEC + e, main_op, reduce_op);
+          }
         }
 #pragma unroll
         for (int u = 0; u < R; ++u) {
@@ -145,26 +166,66 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_reduce_staged_kernel(Store
           }
         }
       }
-    } else {
+    }
+    {
       // whole warps walk the passes together (the shuffles below need all lanes)
-      for (int lr0 = 0; lr0 < nr; lr0 += rpp) {
+      for (int lr0 = lr_begin; lr0 < nr; lr0 += rpp) {
         const int lr   = lr0 + slot;
         const bool ok  = lr < nr;
-        const InT* row = tile + size_t(ok ? lr : nr - 1) * row_len;
+        const Vec* row = tile + size_t(ok ? lr : nr - 1) * nvec;
         State st;
         init_state<OutT, State, isSum>(st, init, lig == 0);
-        int c = lig;
-        for (; c + 3 * G < row_len; c += 4 * G) {
-          InT v[4];
+        // The lane's vectors: lig, lig + G, ... Steps that every lane of the group has (n_full of them,
+        // the same for the whole warp) run four at a time; lanes below n_rem take one more.
+        if (rot == 0) {
+          int c = lig;
+          int j = 0;
+          for (; j + 4 <= n_full; j += 4, c += 4 * G) {
+            Vec v[4];
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            v[k] = row[c + k * G];
+            for (int k = 0; k < 4; ++k)
+              v[k] = row[c + k * G];
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            push_element<OutT, IdxT>(st, v[k], c + k * G, main_op, reduce_op);
+            for (int k = 0; k < 4; ++k) {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e)
+                push_element<OutT, IdxT>(st, v[k].e[e], (c + k * G) * VEC + e, main_op, reduce_op);
+            }
+          }
+          for (; j < n_full + (lig < n_rem ? 1 : 0); ++j, c += G) {
+            const Vec v = row[c];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              push_element<OutT, IdxT>(st, v.e[e], c * VEC + e, main_op, reduce_op);
+          }
+        } else {
+          // counted from the slot's starting point, wrapping at the end of the row
+          int j = 0;
+          for (; j + 4 <= n_full; j += 4) {
+            Vec v[4];
+            int c[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              c[k] = ((j + k) << lg) + lig + shift;
+              c[k] = c[k] >= nvec ? c[k] - nvec : c[k];
+              v[k] = row[c[k]];
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e)
+                push_element<OutT, IdxT>(st, v[k].e[e], c[k] * VEC + e, main_op, reduce_op);
+            }
+          }
+          for (; j < n_full + (lig < n_rem ? 1 : 0); ++j) {
+            int c       = (j << lg) + lig + shift;
+            c           = c >= nvec ? c - nvec : c;
+            const Vec v = row[c];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              push_element<OutT, IdxT>(st, v.e[e], c * VEC + e, main_op, reduce_op);
+          }
         }
-        for (; c < row_len; c += G)
-          push_element<OutT, IdxT>(st, row[c], c, main_op, reduce_op);
         for (int off = G >> 1; off > 0; off >>= 1) {
           State got = shfl_xor_any(st, off);
           st.merge(got, reduce_op);

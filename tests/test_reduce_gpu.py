@@ -303,15 +303,21 @@ def test_rows_tma_staged(cuda, oracle, knobs, rows, cols):
                                           (9999, 33, np.float32), (12346, 65, np.float32), (5003, 129, np.float32),
                                           (3001, 513, np.float32), (2002, 1001, np.float32), (1003, 1023, np.float32),
                                           (20001, 7, np.float64), (5001, 131, np.float64), (30003, 13, np.float16),
-                                          (25001, 9, np.int32)])
+                                          (25001, 9, np.int32),
+                                          # rows on 16-byte boundaries (staged when their length fits the lane groups badly)
+                                          (30001, 8, np.float32), (20001, 36, np.float32), (10001, 96, np.float32),
+                                          (7001, 100, np.float32), (3001, 400, np.float32), (2001, 784, np.float32),
+                                          (1501, 1024, np.float32), (5001, 50, np.float64), (9001, 24, np.float16),
+                                          (9001, 100, np.int32)])
 @pytest.mark.parametrize("tile_kb", [None, "6"])
 def test_rows_staged_odd_widths(cuda, oracle, knobs, rows, cols, dt, tile_kb):
-    """Contiguous rows off 16-byte boundaries through the shared-memory staged kernel, forced onto small inputs:
-    lane-per-row, four rows per lane, 2..32 lanes per row; row counts that leave rows behind the last 16-byte
-    boundary; default and tiny tiles (many tiles per CTA, every ring depth)."""
+    """Contiguous rows through the shared-memory staged kernel, forced onto small inputs: rows off 16-byte
+    boundaries (element loads) and on them (16-byte loads, rotated starts); lane-per-row, four rows per lane,
+    2..32 lanes per row; row counts that leave rows behind the last 16-byte boundary; default and tiny tiles
+    (many tiles per CTA, every ring depth)."""
     if tile_kb is not None and cols * np.dtype(dt).itemsize * 8 > 6 * 1024:
         pytest.skip("eight rows do not fit the tiny tile")
-    knobs(B2R_ROW_STAGED_MIN_KB="0", B2R_ROW_STAGED_WIDE_MIN_KB="0", B2R_ROW_STAGED_KB=tile_kb)
+    knobs(B2R_ROW_STAGED_MIN_KB="1", B2R_ROW_STAGED_WIDE_MIN_KB="1", B2R_ROW_STAGED_ALIGNED="2", B2R_ROW_STAGED_KB=tile_kb)
     t, host = device_synth((rows, cols), dt, 29, "uniform" if dt == np.float16 else "int", -4, 5, cuda)
     out_dt = torch.float32 if dt == np.float16 else None
     got = linalg.reduce(t, linalg.ALONG_ROWS, out_dtype=out_dt)
