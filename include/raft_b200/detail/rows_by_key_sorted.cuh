@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(TPB) rbk_units_kernel(const int* __restrict__ 
 // more lanes per row the warp translates 32 ordinals at once, one per lane, and hands the row
 // numbers out by shuffle; narrower matrices translate per load.
 template <typename DataT, typename WeightT, typename SumT, int VEC>
-__global__ void __launch_bounds__(256) rbk_stream_kernel(typename sum_state<SumT>::type::carry_t* __restrict__ partial,
+__global__ void __launch_bounds__(256, 3) rbk_stream_kernel(typename sum_state<SumT>::type::carry_t* __restrict__ partial,
                                                         const DataT* __restrict__ A,
                                                         int64_t lda,
                                                         const WeightT* __restrict__ weights,
