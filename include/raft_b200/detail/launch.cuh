@@ -297,6 +297,86 @@ inline size_t row_reduce_scratch_bytes(int64_t n_rows, int64_t row_len, size_t i
   return n_seg > 1 ? align_up(size_t(n_rows) * n_seg * sizeof(CarryT), 256) : 0;
 }
 
+// Shape of a launch of the shared-memory staged row kernels (row_reduce_staged.cuh,
+// row_normalize_staged.cuh) over a contiguous matrix.
+struct StagedPlan {
+  bool ok;            // false: the rows do not fit the ring, take another kernel
+  int m;              // every m-th row starts on a 16-byte boundary
+  int64_t n_main;     // rows the staged kernel takes (a multiple of m); the rest goes to a direct kernel
+  int G;              // lanes per row
+  int rot;            // bank rotation per row slot, in vectors
+  int stages;
+  int64_t tile_rows;
+  int64_t rows_per_cta;
+  int64_t ctas;
+  size_t stage_bytes;
+  size_t smem;        // stages x stage_bytes
+};
+
+inline StagedPlan plan_staged_rows(int64_t n_rows, size_t row_bytes, int nvec, bool vec_ok)
+{
+  StagedPlan p{};
+  // every m-th row starts on a boundary
+  size_t gcd16 = 16;
+  while (row_bytes % gcd16 != 0) gcd16 >>= 1;
+  p.m                 = int(16 / gcd16);
+  const int m         = p.m;
+  const size_t budget = size_t(tuning().row_staged_tile_kb) << 10;
+  p.n_main            = n_rows - n_rows % m;
+  const size_t ring   = size_t(tuning().row_staged_ring_kb) << 10;
+  // rows a tile may hold: the budget, less for small inputs so that every CTA still gets a few tiles
+  // (two CTAs resident per SM with a ring of up to 100 KB, else one)
+  const int64_t ctas0 = int64_t(sm_count()) * (ring <= (size_t(104) << 10) ? 2 : 1);
+  int64_t max_rows    = int64_t(budget / row_bytes);
+  const int64_t fit   = p.n_main / (ctas0 * 4);
+  if (max_rows > fit) max_rows = fit;
+  max_rows            = max_rows / m * m;
+  if (max_rows < m) max_rows = m;
+  if (!(size_t(max_rows) * row_bytes <= budget && 2 * (budget + 128) <= ring && p.n_main > 0)) return p;
+  // Lanes per row and rows per tile: a tile is a whole number of passes of the 256 consumers
+  // (256 / G rows each). What a lane does per row besides summing - set-up, shuffles, the store -
+  // weighs more the fewer vectors it gets, so: the FEWEST lanes per row whose tiles still fill
+  // seven tenths of the ring (the bytes in flight), else the choice that fills it best.
+  // A last pass that is at least nine tenths busy counts as whole.
+  int Gs            = 32;
+  int64_t tile_rows = max_rows;  // rows too long for a whole pass: one partial pass with 32 lanes per row
+  size_t best_fill  = 0;
+  for (int g2 = 1; g2 <= 32; g2 <<= 1) {
+    const int64_t rpp = kTmaConsumers / g2;
+    int64_t tr        = max_rows / rpp * rpp;  // rpp is a multiple of 8, so of m
+    if (max_rows * 10 >= ceil_div<int64_t>(max_rows, rpp) * rpp * 9) tr = max_rows;
+    if (tr == 0 || (g2 > 1 && nvec < 2 * g2)) continue;
+    const size_t tile = (size_t(tr) * row_bytes + 127) / 128 * 128;
+    size_t n_st       = ring / tile;
+    n_st              = n_st > size_t(kTmaMaxStages) ? size_t(kTmaMaxStages) : n_st;
+    const size_t fill = n_st * tile;
+    if (fill > best_fill) {
+      best_fill = fill;
+      Gs        = g2;
+      tile_rows = tr;
+    }
+    if (fill * 10 >= ring * 7) break;
+  }
+  // Bank rotation, 16-byte loads only: eight lanes are served at a time, so with fewer than eight
+  // lanes per row they sit on different rows, (row pitch + rot) vectors apart; with that distance
+  // congruent to G modulo 2 G they fall into different banks. Single elements of rows off the
+  // boundaries: the pitch is odd or twice an odd number, at worst a two-way conflict - not worth
+  // the index arithmetic per element.
+  p.rot         = (vec_ok && Gs < 8) ? (Gs - nvec % (2 * Gs) + 2 * Gs) % (2 * Gs) : 0;
+  p.G           = Gs;
+  p.tile_rows   = tile_rows;
+  p.stage_bytes = (size_t(tile_rows) * row_bytes + 127) / 128 * 128;
+  // what keeps HBM busy is the bytes in flight: as many stages as the ring holds
+  int stages    = int(ring / p.stage_bytes);
+  p.stages      = stages > kTmaMaxStages ? kTmaMaxStages : stages;
+  p.smem        = size_t(p.stages) * p.stage_bytes;
+  int64_t rpc   = ceil_div<int64_t>(p.n_main, ctas0);
+  p.rows_per_cta = ceil_div<int64_t>(rpc, tile_rows) * tile_rows;
+  p.ctas        = ceil_div<int64_t>(p.n_main, p.rows_per_cta);
+  p.ok          = true;
+  return p;
+}
+
 // `out` may point to a type other than the accumulator type OutT (what final_op returns).
 template <typename InT,
           typename OutT,
@@ -419,60 +499,12 @@ cudaError_t launch_row_reduce(StoreT* out,
                                  row_len <= tuning().row_staged_aligned_max);
     }
     if (staged) {
-      // every m-th row starts on a boundary
-      size_t gcd16 = 16;
-      while (row_bytes % gcd16 != 0) gcd16 >>= 1;
-      const int m           = int(16 / gcd16);
-      const size_t budget   = size_t(tuning().row_staged_tile_kb) << 10;
-      const int64_t n_main  = n_rows - n_rows % m;
-      const size_t ring     = size_t(tuning().row_staged_ring_kb) << 10;
-      // rows a tile may hold: the budget, less for small inputs so that every CTA still gets a few tiles
-      // (two CTAs resident per SM with a ring of up to 100 KB, else one)
-      const int64_t ctas0 = int64_t(sm_count()) * (ring <= (size_t(104) << 10) ? 2 : 1);
-      int64_t max_rows    = int64_t(budget / row_bytes);
-      const int64_t fit   = n_main / (ctas0 * 4);
-      if (max_rows > fit) max_rows = fit;
-      max_rows            = max_rows / m * m;
-      if (max_rows < m) max_rows = m;
-      if (size_t(max_rows) * row_bytes <= budget && 2 * (budget + 128) <= ring && n_main > 0) {
-        // Lanes per row Gs and rows per tile: a tile is a whole number of passes of the 256 consumers
-        // (256 / Gs rows each). What a lane does per row besides summing - set-up, shuffles, the store -
-        // weighs more the fewer vectors it gets, so: the FEWEST lanes per row whose tiles still fill
-        // seven tenths of the ring (the bytes in flight), else the choice that fills it best.
-        // A last pass that is at least nine tenths busy counts as whole.
-        int Gs            = 32;
-        int64_t tile_rows = max_rows;  // rows too long for a whole pass: one partial pass with 32 lanes per row
-        size_t best_fill  = 0;
-        for (int g2 = 1; g2 <= 32; g2 <<= 1) {
-          const int64_t rpp = kTmaConsumers / g2;
-          int64_t tr        = max_rows / rpp * rpp;  // rpp is a multiple of 8, so of m
-          if (max_rows * 10 >= ceil_div<int64_t>(max_rows, rpp) * rpp * 9) tr = max_rows;
-          if (tr == 0 || (g2 > 1 && nvec < 2 * g2)) continue;
-          const size_t tile = (size_t(tr) * row_bytes + 127) / 128 * 128;
-          size_t n_st       = ring / tile;
-          n_st              = n_st > size_t(kTmaMaxStages) ? size_t(kTmaMaxStages) : n_st;
-          const size_t fill = n_st * tile;
-          if (fill > best_fill) {
-            best_fill = fill;
-            Gs        = g2;
-            tile_rows = tr;
-          }
-          if (fill * 10 >= ring * 7) break;
-        }
-        // Bank rotation, 16-byte loads only: eight lanes are served at a time, so with fewer than eight
-        // lanes per row they sit on different rows, (row pitch + rot) vectors apart; with that distance
-        // congruent to Gs modulo 2 Gs they fall into different banks. Single elements of rows off the
-        // boundaries: the pitch is odd or twice an odd number, at worst a two-way conflict - not worth
-        // the index arithmetic per element.
-        const int rot       = (vec_ok && Gs < 8) ? (Gs - nvec % (2 * Gs) + 2 * Gs) % (2 * Gs) : 0;
-        const size_t stage  = (size_t(tile_rows) * row_bytes + 127) / 128 * 128;
-        // what keeps HBM busy is the bytes in flight: as many stages as the ring holds
-        int stages          = int(ring / stage);
-        stages              = stages > kTmaMaxStages ? kTmaMaxStages : stages;
-        const size_t smem   = size_t(stages) * stage;
-        int64_t rpc             = ceil_div<int64_t>(n_main, ctas0);
-        rpc                     = ceil_div<int64_t>(rpc, tile_rows) * tile_rows;
-        const int64_t ctas      = ceil_div<int64_t>(n_main, rpc);
+      const StagedPlan sp = plan_staged_rows(n_rows, row_bytes, nvec, vec_ok);
+      if (sp.ok) {
+        const int64_t n_main = sp.n_main;
+        const int Gs = sp.G, rot = sp.rot, stages = sp.stages;
+        const int64_t tile_rows = sp.tile_rows, rpc = sp.rows_per_cta, ctas = sp.ctas;
+        const size_t smem = sp.smem;
 #define B2R_LAUNCH_STAGED(VEC_)                                                                              \
   do {                                                                                                       \
     auto kern      = row_reduce_staged_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, StoreT>;     \

@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "launch.cuh"
 #include "ops.cuh"
+#include "row_normalize_staged.cuh"
 
 namespace raft_b200 {
 namespace detail {
@@ -256,6 +257,53 @@ cudaError_t launch_row_normalize(T* out,
   const int vec     = vec_ok ? V16 : 1;
   const int64_t nvec = n_cols / vec;
   const int sms      = sm_count();
+
+  // Rows staged through shared memory in both directions (row_normalize_staged.cuh): rows that do not
+  // start on 16-byte boundaries, and aligned rows whose vector count is no power of two (the lane groups
+  // of the kernels below are). Same size rules as the staged row reduction.
+  if constexpr (V16 > 1 && sizeof(T) >= 2) {
+    const size_t row_bytes = size_t(n_cols) * sizeof(T);
+    bool staged            = tuning().row_staged == 1 && aligned16(in) && aligned16(out) &&
+                  n_cols <= tuning().row_staged_max &&
+                  size_t(n_rows) * row_bytes >=
+                    (size_t(n_cols <= 64 ? tuning().row_staged_min_kb : tuning().row_staged_wide_min_kb) << 10);
+    if (staged && vec_ok) {
+      // measured: the direct kernels hold their own for powers of two and for 3 x 2^k vectors from 48 on
+      const int mode       = tuning().row_staged_aligned;  // 1: by rule, 2: always, 3: never
+      const bool pow2      = (nvec & (nvec - 1)) == 0;
+      const bool three_2k  = nvec >= 48 && nvec % 3 == 0 && ((nvec / 3) & (nvec / 3 - 1)) == 0;
+      staged = mode == 2 || (mode == 1 && !pow2 && !three_2k && n_cols <= tuning().row_staged_aligned_max);
+    } else if (staged) {
+      staged = row_bytes >= 12;  // one or two elements per row: nothing to gain
+    }
+    if (staged) {
+      const StagedPlan sp = plan_staged_rows(n_rows, row_bytes, int(nvec), vec_ok);
+      const size_t smem   = sp.smem + size_t(sp.stages) * size_t((sp.tile_rows + 31) / 32) * sizeof(unsigned);
+      if (sp.ok && smem <= (size_t(108) << 10)) {
+#define B2R_NORMALIZE_STAGED(VEC_)                                                                            \
+  do {                                                                                                        \
+    auto kern      = row_normalize_staged_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_>;                   \
+    cudaError_t ea = ensure_dynamic_smem(kern, smem);                                                         \
+    if (ea != cudaSuccess) return ea;                                                                         \
+    kern<<<unsigned(sp.ctas), kTmaThreads, smem, stream>>>(out, in, sp.n_main, int(n_cols), init, eps, main_op, \
+                                                          reduce_op, final_op, sp.G, sp.rot, int(sp.tile_rows), \
+                                                          sp.rows_per_cta, sp.stages);                        \
+  } while (0)
+        if (vec_ok) {
+          B2R_NORMALIZE_STAGED(V16);
+        } else {
+          B2R_NORMALIZE_STAGED(1);
+        }
+#undef B2R_NORMALIZE_STAGED
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess || sp.n_main == n_rows) return e;
+        // the rows behind the last 16-byte boundary: the direct kernels
+        return launch_row_normalize<T, IdxT, MainOp, ReduceOp, FinalOp>(out + sp.n_main * n_cols, in + sp.n_main * n_cols,
+                                                                        n_rows - sp.n_main, n_cols, init, eps, main_op,
+                                                                        reduce_op, final_op, stream);
+      }
+    }
+  }
 
 #define B2R_NORMALIZE_REG(VEC_, CPL_)                                                                     \
   do {                                                                                                    \

@@ -105,3 +105,58 @@ def test_argument_checks(cuda):
         linalg.row_normalize(t, "L0")
     with pytest.raises(ValueError):
         linalg.row_normalize(t.t(), "L2")
+
+
+@pytest.mark.parametrize("rows,cols,dt,tol", [(100003, 1, np.float32, 1e-5), (70001, 2, np.float32, 1e-5),
+                                              (50002, 3, np.float32, 1e-5), (33333, 7, np.float32, 1e-5),
+                                              (20001, 17, np.float32, 1e-5), (9999, 33, np.float32, 1e-5),
+                                              (12346, 65, np.float32, 1e-5), (5003, 129, np.float32, 1e-5),
+                                              (3001, 513, np.float32, 1e-5), (2002, 1001, np.float32, 1e-5),
+                                              (20001, 7, np.float64, 1e-8), (5001, 131, np.float64, 1e-8),
+                                              # rows on 16-byte boundaries
+                                              (30001, 8, np.float32, 1e-5), (20001, 36, np.float32, 1e-5),
+                                              (10001, 96, np.float32, 1e-5), (7001, 100, np.float32, 1e-5),
+                                              (3001, 400, np.float32, 1e-5), (2001, 784, np.float32, 1e-5),
+                                              (5001, 50, np.float64, 1e-8)])
+@pytest.mark.parametrize("norm", NORMS)
+@pytest.mark.parametrize("tile_kb", [None, "6"])
+def test_staged(cuda, oracle, ref, knobs, rows, cols, dt, tol, norm, tile_kb):
+    """The shared-memory staged kernel (block copies in both directions), forced onto small inputs: rows off
+    and on 16-byte boundaries, 1..32 lanes per row, rows behind the last boundary, default and tiny tiles;
+    rows at or below eps stay untouched (tiles with such rows are stored row by row), in place as well."""
+    knobs(B2R_ROW_STAGED_MIN_KB="1", B2R_ROW_STAGED_WIDE_MIN_KB="1", B2R_ROW_STAGED_ALIGNED="2",
+          B2R_ROW_STAGED_KB=tile_kb)
+    t, host = device_synth((rows, cols), dt, 77, "uniform", -10, 10, cuda)
+    ours = linalg.row_normalize(t, norm)
+    exp = oracle.row_normalize(host, norm)
+    oracle.assert_approx(exp, ours.cpu().numpy(), tol, "staged vs oracle")
+    knobs(B2R_ROW_STAGED="2")
+    direct = linalg.row_normalize(t, norm)
+    oracle.assert_approx(direct.cpu().numpy(), ours.cpu().numpy(), tol * 0.1, "staged vs direct")
+    knobs(B2R_ROW_STAGED=None)
+    # rows that must not be written: scattered zero rows and one whole stretch of them
+    t[::97] = 0.0
+    t[rows // 2: rows // 2 + 700] = 0.0
+    host = t.cpu().numpy()
+    out = torch.full_like(t, 7.0)
+    linalg.row_normalize(t, norm, out=out)
+    exp = oracle.row_normalize(host, norm, prev=np.full_like(host, 7.0))
+    oracle.assert_approx(exp, out.cpu().numpy(), tol, "sentinel rows")
+    assert torch.all(out[::97] == 7.0)
+    # in place
+    keep = t.clone()
+    linalg.row_normalize(t, norm, out=t)
+    exp = oracle.row_normalize(host, norm, prev=host.copy())
+    oracle.assert_approx(exp, t.cpu().numpy(), tol, "in place")
+    assert torch.equal(t[::97], keep[::97])
+
+
+def test_staged_full_size(cuda, oracle):
+    """12 000 002 x 23 fp32 (1.1 GB, default policy, two rows behind the last boundary), L2: unit rows."""
+    t, _ = device_synth((12000002, 23), np.float32, 78, "uniform", -10, 10, cuda)
+    out = linalg.row_normalize(t, "L2")
+    n = torch.linalg.vector_norm(out.double(), dim=1)
+    assert float((n - 1.0).abs().max()) < 1e-5
+    norms = torch.linalg.vector_norm(t.double(), dim=1)
+    for c in (0, 11, 22):
+        assert float((out[:, c].double() * norms - t[:, c].double()).abs().max()) < 1e-4
