@@ -131,8 +131,8 @@ struct Tuning {
   int row_staged_aligned   = 1;     // B2R_ROW_STAGED_ALIGNED aligned rows staged 1: when the direct kernel would leave a tenth of its load slots empty, 2: always, 3: never
   int row_staged_aligned_max = 800;  // B2R_ROW_STAGED_ALIGNED_MAX longest aligned row (elements) staged by rule 1
   int row_staged_max       = 1024;   // B2R_ROW_STAGED_MAX longest such row (elements) that is staged
-  int row_staged_min_kb    = 8192;  // B2R_ROW_STAGED_MIN_KB smallest matrix (KiB) that is staged, rows up to 64 elements
-  int row_staged_wide_min_kb = 131072;  // B2R_ROW_STAGED_WIDE_MIN_KB the same for longer rows (the direct kernels ramp up faster)
+  int row_staged_min_kb    = 32768;  // B2R_ROW_STAGED_MIN_KB smallest matrix (KiB) that is staged: rows up to 64 elements, aligned rows up to 512
+  int row_staged_wide_min_kb = 131072;  // B2R_ROW_STAGED_WIDE_MIN_KB the same for rows of more than 512 elements; half of it for unaligned rows of 65..512
   int row_staged_tile_kb   = 48;    // B2R_ROW_STAGED_KB tile size of that ring, KiB
   int row_staged_ring_kb   = 100;   // B2R_ROW_STAGED_RING_KB shared memory of one CTA's ring, KiB (100: two CTAs per SM)
 };
@@ -295,6 +295,16 @@ inline size_t row_reduce_scratch_bytes(int64_t n_rows, int64_t row_len, size_t i
   }
   if (n_seg_out) *n_seg_out = n_seg;
   return n_seg > 1 ? align_up(size_t(n_rows) * n_seg * sizeof(CarryT), 256) : 0;
+}
+
+// Smallest matrix (bytes) for which the staged row reduction beats the direct kernels, measured with a
+// cold L2: the ring needs a few tiles per CTA to get going, the direct kernels ramp up faster.
+inline size_t staged_min_bytes(int64_t row_len, bool vec_ok)
+{
+  const size_t narrow = size_t(tuning().row_staged_min_kb) << 10;
+  const size_t wide   = size_t(tuning().row_staged_wide_min_kb) << 10;
+  if (row_len <= 64 || (vec_ok && row_len <= 512)) return narrow;
+  return row_len <= 512 ? wide / 2 : wide;
 }
 
 // Shape of a launch of the shared-memory staged row kernels (row_reduce_staged.cuh,
@@ -488,8 +498,7 @@ cudaError_t launch_row_reduce(StoreT* out,
     const size_t row_bytes = size_t(row_len) * sizeof(InT);
     bool staged            = tuning().row_staged == 1 && ld == row_len && aligned16(data) &&
                   row_len <= tuning().row_staged_max &&
-                  size_t(n_rows) * row_bytes >=
-                    (size_t(row_len <= 64 ? tuning().row_staged_min_kb : tuning().row_staged_wide_min_kb) << 10);
+                  size_t(n_rows) * row_bytes >= staged_min_bytes(row_len, vec_ok);
     if (staged && vec_ok) {
       // slots of the direct kernel's lane groups that would stay empty
       const int64_t slots = int64_t(G) * cpl * ceil_div<int64_t>(nvec, int64_t(G) * cpl);

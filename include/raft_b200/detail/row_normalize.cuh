@@ -260,13 +260,16 @@ cudaError_t launch_row_normalize(T* out,
 
   // Rows staged through shared memory in both directions (row_normalize_staged.cuh): rows that do not
   // start on 16-byte boundaries, and aligned rows whose vector count is no power of two (the lane groups
-  // of the kernels below are). Same size rules as the staged row reduction.
+  // of the kernels below are), large matrices only.
   if constexpr (V16 > 1 && sizeof(T) >= 2) {
     const size_t row_bytes = size_t(n_cols) * sizeof(T);
     bool staged            = tuning().row_staged == 1 && aligned16(in) && aligned16(out) &&
                   n_cols <= tuning().row_staged_max &&
-                  size_t(n_rows) * row_bytes >=
-                    (size_t(n_cols <= 64 ? tuning().row_staged_min_kb : tuning().row_staged_wide_min_kb) << 10);
+                  // measured with a cold L2: 64 MB for rows off the boundaries and short aligned rows, 256 MB
+                  // for longer aligned rows (the direct kernels are better there to begin with)
+                  size_t(n_rows) * row_bytes >= 2 * (size_t(vec_ok && n_cols > 64 ? tuning().row_staged_wide_min_kb
+                                                                                   : tuning().row_staged_min_kb)
+                                                     << 10);
     if (staged && vec_ok) {
       // measured: the direct kernels hold their own for powers of two and for 3 x 2^k vectors from 48 on
       const int mode       = tuning().row_staged_aligned;  // 1: by rule, 2: always, 3: never
