@@ -50,6 +50,7 @@ WORKLOADS = {
     "mapsum": (1_048_576, 1024, "mapThenSumReduce identity fp32, 2^30 elements U[-1,1) seed 7"),
     "colsbykey": (2_000, 200_000, "reduce_cols_by_key fp32 2000x200000 U[-1,1) seed 8, int32 keys U[0,128) seed 9"),
     "oddrows": (8_000_000, 31, "row sum of rows off 16-byte boundaries fp32 8000000x31 U[-1,1) seed 10"),
+    "norm96": (2_500_000, 96, "L2 row norm with sqrt fp32 2500000x96 (24 vectors per row: no power of two) N(0,1) seed 11"),
 }
 COL_NKEYS = 128
 NKEYS = 1024
@@ -58,7 +59,7 @@ NKEYS = 1024
 def algorithmic_bytes(name):
     rows, cols, _ = WORKLOADS[name]
     inp = rows * cols * 4
-    if name in ("c1", "c2", "c2sq", "oddrows"):
+    if name in ("c1", "c2", "c2sq", "oddrows", "norm96"):
         return inp + rows * 4
     if name in ("c3", "c3mean"):
         return inp + cols * 4
@@ -77,7 +78,7 @@ def algorithmic_bytes(name):
 
 def launches_per_step(name):
     return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 6, "normalize": 1, "mapsum": 2, "colsbykey": 3,
-            "oddrows": 1}[name]
+            "oddrows": 1, "norm96": 1}[name]
 
 
 class Workload:
@@ -97,6 +98,8 @@ class Workload:
             linalg.synth_fill(self.data, 0, "uniform", -1, 1, first_index=base)
         elif name == "oddrows":
             linalg.synth_fill(self.data, 10, "uniform", -1, 1, first_index=base)
+        elif name == "norm96":
+            linalg.synth_fill(self.data, 11, "normal", first_index=base)
         elif name in ("c2", "c2sq"):
             linalg.synth_fill(self.data, 1, "normal", first_index=base)
         elif name in ("c3", "c3mean"):
@@ -115,7 +118,7 @@ class Workload:
             linalg.synth_fill(self.data, 8, "uniform", -1, 1, first_index=base)
             self.keys = torch.empty((cols,), dtype=torch.int32, device=device)
             linalg.synth_fill(self.keys, 9, "int", 0, COL_NKEYS)  # the columns are not sharded: same keys on every rank
-        if name in ("c1", "c2", "c2sq", "oddrows"):
+        if name in ("c1", "c2", "c2sq", "oddrows", "norm96"):
             self.out = torch.empty(rows, dtype=torch.float32, device=device)
         elif name in ("c3", "c3mean"):
             self.out = torch.empty(cols, dtype=torch.float32, device=device)
@@ -154,7 +157,7 @@ class Workload:
         if self.impl == "ours":
             if n in ("c1", "oddrows"):
                 la.coalesced_reduction(data, self.out)
-            elif n == "c2":
+            elif n in ("c2", "norm96"):
                 la.norm(data, "L2", la.ALONG_ROWS, self.out, fin_op="sqrt")
             elif n == "c2sq":
                 la.norm(data, "L2", la.ALONG_ROWS, self.out)
@@ -193,7 +196,7 @@ class Workload:
             st = 0
             if n in ("c1", "oddrows"):
                 st = r.reduce(data, L.ALONG_ROWS, self.out)
-            elif n == "c2":
+            elif n in ("c2", "norm96"):
                 st = r.reduce(data, L.ALONG_ROWS, self.out, main_op=L.MAIN_SQ, final_op=L.FINAL_SQRT)
             elif n == "c2sq":
                 st = r.reduce(data, L.ALONG_ROWS, self.out, main_op=L.MAIN_SQ)
@@ -319,12 +322,12 @@ def cpu_baseline(name, budget_rows=None):
     sample_rows = min(rows, budget_rows or {"c1": 4096, "c2": 1_000_000, "c2sq": 1_000_000, "c3": 2_000_000,
                                             "c3mean": 2_000_000, "c4": 2_000_000, "c5": 1_000_000,
                                             "normalize": 100_000, "mapsum": 262_144, "colsbykey": 500,
-                                            "oddrows": 4_000_000}[name])
+                                            "oddrows": 4_000_000, "norm96": 1_250_000}[name])
     seed, kind, lo, hi = {"c1": (0, "uniform", -1, 1), "c2": (1, "normal", 0, 1), "c2sq": (1, "normal", 0, 1),
                           "c3": (2, "uniform", 0, 1), "c3mean": (2, "uniform", 0, 1), "c4": (3, "int", 0, 16),
                           "c5": (4, "normal", 0, 1), "normalize": (6, "uniform", -10, 10),
                           "mapsum": (7, "uniform", -1, 1), "colsbykey": (8, "uniform", -1, 1),
-                          "oddrows": (10, "uniform", -1, 1)}[name]
+                          "oddrows": (10, "uniform", -1, 1), "norm96": (11, "normal", 0, 1)}[name]
     data = o.synth((sample_rows, cols), np.float32, seed, kind, lo, hi)
     keys = o.synth((sample_rows,), np.int32, 5, "int", 0, NKEYS) if name == "c5" else None
     ckeys = o.synth((cols,), np.int32, 9, "int", 0, COL_NKEYS) if name == "colsbykey" else None
@@ -332,7 +335,7 @@ def cpu_baseline(name, budget_rows=None):
     def once():
         if name in ("c1", "oddrows"):
             o.omp_row_sum(data)
-        elif name == "c2":
+        elif name in ("c2", "norm96"):
             o.omp_row_sum(data, square=True, root=True)
         elif name == "c2sq":
             o.omp_row_sum(data, square=True)
@@ -560,7 +563,7 @@ def main():
     line = {"metric": "hbm_gb_per_s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4", "normalize", "colsbykey", "oddrows") or world == 1
+            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4", "normalize", "colsbykey", "oddrows", "norm96") or world == 1
                                                         else "per-GPU partials + NCCL all-reduce inside the step"),
                        "l2": "L2 flushed by a 378 MB write before every step" if flush
                        else f"input {rows * cols * 4 >> 20} MB per GPU > 126 MB L2"},
@@ -581,7 +584,7 @@ def main():
         table = {}
         del w
         torch.cuda.empty_cache()
-        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5", "normalize", "mapsum", "colsbykey", "oddrows"):
+        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5", "normalize", "mapsum", "colsbykey", "oddrows", "norm96"):
             r, c, _ = WORKLOADS[cn]
             ent = {}
             for impl in ("ours", "reference"):

@@ -458,7 +458,8 @@ cudaError_t launch_row_reduce(StoreT* out,
   // scalar path (rows that do not start on 16-byte boundaries): a load brings 4 bytes instead of 16, so
   // a lane takes four elements of a row whenever the row has them and keeps 32 loads in flight
   if (cpl == 0 && !vec_ok) cpl = nvec >= 4 ? 4 : (nvec >= 2 ? 2 : 1);
-  if (cpl == 0) cpl = nvec >= 32 ? 4 : (nvec >= 8 ? 2 : 1);
+  // (rows of exactly four vectors: a lane takes the whole row - measured 12.3 against 14.3 us at 400 000 x 16 fp32)
+  if (cpl == 0) cpl = nvec >= 32 ? 4 : (nvec >= 8 ? 2 : (nvec == 4 ? 4 : 1));
   if (cpl != 1 && cpl != 2 && cpl != 4) cpl = 1;
   unsigned g           = next_pow2(unsigned(nvec > 0 ? ceil_div<int>(nvec, cpl) : 1));
   const int G          = int(g > 32u ? 32u : g);
