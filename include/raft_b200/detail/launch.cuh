@@ -131,8 +131,8 @@ struct Tuning {
   int row_staged_aligned   = 1;     // B2R_ROW_STAGED_ALIGNED aligned rows staged 1: when the direct kernel would leave a tenth of its load slots empty, 2: always, 3: never
   int row_staged_aligned_max = 800;  // B2R_ROW_STAGED_ALIGNED_MAX longest aligned row (elements) staged by rule 1
   int row_staged_max       = 1024;   // B2R_ROW_STAGED_MAX longest such row (elements) that is staged
-  int row_staged_min_kb    = 32768;  // B2R_ROW_STAGED_MIN_KB smallest matrix (KiB) that is staged: rows up to 64 elements, aligned rows up to 512
-  int row_staged_wide_min_kb = 131072;  // B2R_ROW_STAGED_WIDE_MIN_KB the same for rows of more than 512 elements; half of it for unaligned rows of 65..512
+  int row_staged_min_kb    = 32768;  // B2R_ROW_STAGED_MIN_KB smallest matrix (KiB) that is staged: aligned rows up to 64 elements; twice that off the boundaries
+  int row_staged_wide_min_kb = 131072;  // B2R_ROW_STAGED_WIDE_MIN_KB the same for longer rows off the boundaries; twice that on them
   int row_staged_tile_kb   = 48;    // B2R_ROW_STAGED_KB tile size of that ring, KiB
   int row_staged_ring_kb   = 100;   // B2R_ROW_STAGED_RING_KB shared memory of one CTA's ring, KiB (100: two CTAs per SM)
 };
@@ -303,8 +303,10 @@ inline size_t staged_min_bytes(int64_t row_len, bool vec_ok)
 {
   const size_t narrow = size_t(tuning().row_staged_min_kb) << 10;
   const size_t wide   = size_t(tuning().row_staged_wide_min_kb) << 10;
-  if (row_len <= 64 || (vec_ok && row_len <= 512)) return narrow;
-  return row_len <= 512 ? wide / 2 : wide;
+  // rows up to 64 elements: 32 MB on 16-byte boundaries, 64 MB off them; longer rows: 256 MB and 128 MB
+  // (the direct kernels are at their best on long aligned rows)
+  if (row_len <= 64) return vec_ok ? narrow : 2 * narrow;
+  return vec_ok ? 2 * wide : wide;
 }
 
 // Shape of a launch of the shared-memory staged row kernels (row_reduce_staged.cuh,

@@ -133,9 +133,16 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
         init_state<OutT, State, isSum>(st[u], init, lig == 0);
       // CPL chunks of every row per lane and pass: U * CPL loads are in flight per lane, and the
       // more of a row one lane sums by itself the fewer exchanges the reduction below needs
-      for (int c0 = lig; c0 < nvec; c0 += G * CPL) {
+      // (the pass structure is the same for every lane of the warp - a pass is "full" only if it is for
+      // the whole group - so a row length that is no multiple of G * CPL costs one masked pass, not two
+      // serialised ones)
+      for (int cb = 0; cb < nvec; cb += G * CPL) {
+        const int c0 = cb + lig;
+        if constexpr (CPL == 1) {
+          if (c0 >= nvec) break;  // one chunk per lane and pass: a lane beyond the row's end is simply done
+        }
         VecOf<InT, VEC> v[U][CPL];
-        if (valid == U && c0 + (CPL - 1) * G < nvec) {
+        if (valid == U && (CPL == 1 || cb + CPL * G <= nvec)) {
 #pragma unroll
           for (int u = 0; u < U; ++u) {
 #pragma unroll
@@ -159,7 +166,7 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
 #pragma unroll
             for (int k = 0; k < CPL; ++k) {
               const int c  = c0 + k * G;
-              const int cc = c < nvec ? c : c0;  // re-read a valid chunk, ignored below
+              const int cc = c < nvec ? c : cb;  // re-read a valid chunk, ignored below
               v[u][k]      = load_stream<InT, VEC>(base + uu * step + int64_t(cc) * VEC);
             }
           }
@@ -223,8 +230,9 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
           rp += head;
         }
       }
+      // full passes for the whole group first (the same count for every lane), then one masked pass
       int c = lig;
-      for (; c + (U - 1) * G < nv; c += U * G) {
+      for (int cb = 0; cb + U * G <= nv; cb += U * G, c += U * G) {
         VecOf<InT, VEC> v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -236,12 +244,12 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
             push_element<OutT, IdxT>(st[u], v[u].e[e], head + (c + u * G) * VEC + e, main_op, reduce_op);
         }
       }
-      if (c < nv) {
-        // ragged end of the row: the up to U - 1 chunks that are left go out together, not one by one
+      if (c - lig < nv) {
+        // ragged end of the row: the chunks that are left go out together, not one by one
         VecOf<InT, VEC> v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          v[u] = load_stream<InT, VEC>(rp + int64_t(c + u * G < nv ? c + u * G : c) * VEC);
+          v[u] = load_stream<InT, VEC>(rp + int64_t(c + u * G < nv ? c + u * G : c - lig) * VEC);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           if (c + u * G < nv) {
