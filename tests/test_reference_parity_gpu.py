@@ -63,8 +63,9 @@ def test_strided_against_reference(cuda, oracle, ref, main, red, fin, scalar, ro
     ours = linalg.reduce(d, apply, main_op=main, reduce_op=red, final_op=fin, final_scalar=scalar)
     exp = oracle.reduce(host, apply=apply, layout=layout, main_op=main, reduce_op=red, final_op=fin, final_scalar=scalar)
     # the reference's strided sum adds per-block results with fp32 atomics in scheduling order
-    # (linalg/detail/strided_reduction.cuh:54-76): with 200000 rows it is only good to ~5e-5
-    ref_tol = 1e-5 if rows <= 20000 else 2e-4
+    # (linalg/detail/strided_reduction.cuh:54-76): its error varies from run to run and grows with the
+    # rows - with 200000 of them it is only good to ~5e-5, and 12345 have missed 1e-5 once
+    ref_tol = 1e-5 if rows <= 2000 else (5e-5 if rows <= 20000 else 2e-4)
     oracle.assert_approx(exp, theirs.cpu().numpy(), ref_tol, "reference vs oracle")
     oracle.assert_approx(theirs.cpu().numpy(), ours.cpu().numpy(), ref_tol, "ours vs reference")
     oracle.assert_approx(exp, ours.cpu().numpy(), 1e-5, "ours vs oracle")
