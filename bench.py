@@ -50,6 +50,7 @@ WORKLOADS = {
     "mapsum": (1_048_576, 1024, "mapThenSumReduce identity fp32, 2^30 elements U[-1,1) seed 7"),
     "colsbykey": (2_000, 200_000, "reduce_cols_by_key fp32 2000x200000 U[-1,1) seed 8, int32 keys U[0,128) seed 9"),
     "oddrows": (8_000_000, 31, "row sum of rows off 16-byte boundaries fp32 8000000x31 U[-1,1) seed 10"),
+    "normalize100": (2_500_000, 100, "row_normalize L2 fp32 2500000x100 (25 vectors per row) U[-10,10) seed 12 (read + write)"),
     "norm96": (2_500_000, 96, "L2 row norm with sqrt fp32 2500000x96 (24 vectors per row: no power of two) N(0,1) seed 11"),
 }
 COL_NKEYS = 128
@@ -67,7 +68,7 @@ def algorithmic_bytes(name):
         return inp + rows * 8
     if name == "c5":
         return inp + rows * 4 + NKEYS * cols * 4 + NKEYS * 8
-    if name == "normalize":
+    if name in ("normalize", "normalize100"):
         return 2 * inp
     if name == "mapsum":
         return inp + 4
@@ -78,7 +79,7 @@ def algorithmic_bytes(name):
 
 def launches_per_step(name):
     return {"c1": 1, "c2": 1, "c2sq": 1, "c3": 2, "c3mean": 2, "c4": 1, "c5": 6, "normalize": 1, "mapsum": 2, "colsbykey": 3,
-            "oddrows": 1, "norm96": 1}[name]
+            "oddrows": 1, "norm96": 1, "normalize100": 1}[name]
 
 
 class Workload:
@@ -112,6 +113,8 @@ class Workload:
             linalg.synth_fill(self.keys, 5, "int", 0, NKEYS, first_index=first_row)
         elif name == "normalize":
             linalg.synth_fill(self.data, 6, "uniform", -10, 10, first_index=base)
+        elif name == "normalize100":
+            linalg.synth_fill(self.data, 12, "uniform", -10, 10, first_index=base)
         elif name == "mapsum":
             linalg.synth_fill(self.data, 7, "uniform", -1, 1, first_index=base)
         elif name == "colsbykey":
@@ -127,7 +130,7 @@ class Workload:
         elif name == "c5":
             self.out = torch.empty((NKEYS, cols), dtype=torch.float32, device=device)
             self.counts = torch.empty(NKEYS, dtype=torch.int64, device=device)
-        elif name == "normalize":
+        elif name in ("normalize", "normalize100"):
             self.out = torch.zeros_like(self.data)
         elif name == "mapsum":
             self.out = torch.zeros(1, dtype=torch.float32, device=device)
@@ -182,7 +185,7 @@ class Workload:
                     import torch.distributed as dist
                     dist.all_reduce(self.out)     # 1024 x 128 fp32 partial tables
                     dist.all_reduce(self.counts)  # 1024 int64 counts
-            elif n == "normalize":
+            elif n in ("normalize", "normalize100"):
                 la.row_normalize(data, "L2", out=self.out)
             elif n == "colsbykey":
                 la.reduce_cols_by_key(data, self.keys, out=self.out)
@@ -210,7 +213,7 @@ class Workload:
                               init=float("inf"))
             elif n == "c5":
                 st = r.rows_by_key(self.out, data, self.keys if keys is None else keys, NKEYS)
-            elif n == "normalize":
+            elif n in ("normalize", "normalize100"):
                 st = r.row_normalize(self.out, data, "L2")
             elif n == "mapsum":
                 st = r.map_then_sum_reduce(self.out, data)
@@ -322,12 +325,14 @@ def cpu_baseline(name, budget_rows=None):
     sample_rows = min(rows, budget_rows or {"c1": 4096, "c2": 1_000_000, "c2sq": 1_000_000, "c3": 2_000_000,
                                             "c3mean": 2_000_000, "c4": 2_000_000, "c5": 1_000_000,
                                             "normalize": 100_000, "mapsum": 262_144, "colsbykey": 500,
-                                            "oddrows": 4_000_000, "norm96": 1_250_000}[name])
+                                            "oddrows": 4_000_000, "norm96": 1_250_000,
+                                            "normalize100": 1_000_000}[name])
     seed, kind, lo, hi = {"c1": (0, "uniform", -1, 1), "c2": (1, "normal", 0, 1), "c2sq": (1, "normal", 0, 1),
                           "c3": (2, "uniform", 0, 1), "c3mean": (2, "uniform", 0, 1), "c4": (3, "int", 0, 16),
                           "c5": (4, "normal", 0, 1), "normalize": (6, "uniform", -10, 10),
                           "mapsum": (7, "uniform", -1, 1), "colsbykey": (8, "uniform", -1, 1),
-                          "oddrows": (10, "uniform", -1, 1), "norm96": (11, "normal", 0, 1)}[name]
+                          "oddrows": (10, "uniform", -1, 1), "norm96": (11, "normal", 0, 1),
+                          "normalize100": (12, "uniform", -10, 10)}[name]
     data = o.synth((sample_rows, cols), np.float32, seed, kind, lo, hi)
     keys = o.synth((sample_rows,), np.int32, 5, "int", 0, NKEYS) if name == "c5" else None
     ckeys = o.synth((cols,), np.int32, 9, "int", 0, COL_NKEYS) if name == "colsbykey" else None
@@ -345,7 +350,7 @@ def cpu_baseline(name, budget_rows=None):
             o.omp_row_argmin(data)
         elif name == "c5":
             o.omp_rows_by_key(data, keys, NKEYS)
-        elif name == "normalize":
+        elif name in ("normalize", "normalize100"):
             o.row_normalize(data, "L2")
         elif name == "mapsum":
             float(o.omp_row_sum(data).astype(np.float64).sum())  # rows in parallel, then the row sums
@@ -563,7 +568,7 @@ def main():
     line = {"metric": "hbm_gb_per_s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4", "normalize", "colsbykey", "oddrows", "norm96") or world == 1
+            "config": {"workload": desc, "rows_per_gpu": rows, "cols": cols, "sharding": f"rows x{world}, " + ("no collective" if name in ("c1", "c2", "c2sq", "c4", "normalize", "colsbykey", "oddrows", "norm96", "normalize100") or world == 1
                                                         else "per-GPU partials + NCCL all-reduce inside the step"),
                        "l2": "L2 flushed by a 378 MB write before every step" if flush
                        else f"input {rows * cols * 4 >> 20} MB per GPU > 126 MB L2"},
@@ -584,7 +589,7 @@ def main():
         table = {}
         del w
         torch.cuda.empty_cache()
-        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5", "normalize", "mapsum", "colsbykey", "oddrows", "norm96"):
+        for cn in ("c1", "c2sq", "c2", "c3", "c3mean", "c4", "c5", "normalize", "mapsum", "colsbykey", "oddrows", "norm96", "normalize100"):
             r, c, _ = WORKLOADS[cn]
             ent = {}
             for impl in ("ours", "reference"):
