@@ -7,7 +7,7 @@
 // rows is a multiple of 16 bytes long. One producer thread copies such blocks into a ring of
 // shared-memory stages with cp.async.bulk (no register, no alignment concern per row), and the
 // consumers read single elements out of shared memory, where alignment costs nothing: G lanes per
-// row (G = 1 for rows up to 32 elements: a lane sums its row alone, no shuffle at all), lanes of a
+// row (G = 1 while 256 rows fit a tile - 48 fp32: a lane sums its row alone, no shuffle at all), lanes of a
 // warp on consecutive rows, so that for an odd row length all 32 lanes hit different banks.
 // The results of a warp are consecutive rows: one coalesced store.
 //
