@@ -123,10 +123,13 @@ struct Tuning {
   int col_tma_tile_kb      = 32;    // B2R_COL_TMA_KB tile size of the TMA ring, KiB
   int col_tma2d_min_mb     = 256;   // B2R_COL_TMA2D_MB smallest matrix (MiB) for the tiled-TMA kernel of wide matrices
   int tma_stages           = 4;     // B2R_TMA_STAGES stages of the TMA ring (2..8)
-  int row_tma              = 0;     // B2R_ROW_TMA    1: TMA-staged tiles for short contiguous rows
+  int row_tma              = 0;     // B2R_ROW_TMA    ring kernel for short contiguous rows: unset = by shape, 1: wherever it fits, 2: never
+  int row_ring_min_vec     = 8;     // B2R_ROW_RING_MINVEC shortest row (16-byte vectors) that takes the ring kernel by itself
+  int row_ring_max_vec     = 128;   // B2R_ROW_RING_MAXVEC longest such row
+  int row_ring_min_mb      = 1024;  // B2R_ROW_RING_MIN_MB smallest matrix (MiB) that takes it by itself
   int row_shifted_min      = 48;    // B2R_ROW_SHIFTED_MIN shortest row off 16-byte boundaries that takes aligned vector loads
-  int row_tma_tile_kb      = 16;    // B2R_ROW_TMA_KB tile size of the row kernel's TMA ring, KiB
-  int row_tma_stages       = 3;     // B2R_ROW_TMA_STAGES
+  int row_tma_tile_kb      = 32;    // B2R_ROW_TMA_KB tile size of the row kernel's ring, KiB
+  int row_tma_stages       = 4;     // B2R_ROW_TMA_STAGES
   int row_bpc_mode         = 1;     // B2R_ROW_BPC row batches per CTA 1: a multiple of 8 only when that costs under 7 %, 2: always a multiple of 8, 3: odd
   int row_staged           = 1;     // B2R_ROW_STAGED  1: shared-memory staging for contiguous rows off 16-byte boundaries, 2: off
   int row_staged_aligned   = 1;     // B2R_ROW_STAGED_ALIGNED aligned rows staged 1: when the direct kernel would leave a tenth of its load slots empty, 2: always, 3: never
@@ -166,6 +169,9 @@ inline Tuning read_tuning_from_env()
   if (x.tma_stages < 2) x.tma_stages = 2;
   if (x.tma_stages > 8) x.tma_stages = 8;
   x.row_tma              = env_int("B2R_ROW_TMA", x.row_tma);
+  x.row_ring_min_vec     = env_int("B2R_ROW_RING_MINVEC", x.row_ring_min_vec);
+  x.row_ring_max_vec     = env_int("B2R_ROW_RING_MAXVEC", x.row_ring_max_vec);
+  x.row_ring_min_mb      = env_int("B2R_ROW_RING_MIN_MB", x.row_ring_min_mb);
   x.row_shifted_min      = env_int("B2R_ROW_SHIFTED_MIN", x.row_shifted_min);
   x.row_tma_tile_kb      = env_int("B2R_ROW_TMA_KB", x.row_tma_tile_kb);
   x.row_tma_stages       = env_int("B2R_ROW_TMA_STAGES", x.row_tma_stages);
@@ -469,28 +475,54 @@ cudaError_t launch_row_reduce(StoreT* out,
   const int G          = int(g > 32u ? 32u : g);
   const bool chunks    = nvec >= G * cpl * tuning().row_chunk_threshold;
   const int gpw        = 32 / G;
-  // TMA-staged variant: short contiguous rows, plenty of them
+  // Ring variant (row_reduce_tma.cuh): short contiguous rows, plenty of them - one pass of G x cpl chunks per
+  // row out of shared-memory tiles that a producer thread keeps filled. Chosen by itself for rows whose vector
+  // count is exactly G x cpl (a power of two; other lengths leave lanes idle in the consumers, which are bound
+  // by instruction issue: 24 / 48 / 96 / 192 columns measured 4.5-5.1 TB/s against 6.5 direct), between
+  // `row_ring_min_vec` and `row_ring_max_vec` vectors, in matrices of at least `row_ring_min_mb` MiB. Measured,
+  // fp32, TB/s ring / direct: 1 GiB of rows of 32 columns 6.5 / 6.1, 64: 6.55 / 6.3, 128: 6.6 / 6.3, 256: 6.6 / 6.4,
+  // 512: 6.6 / 6.5; 2 GiB x 64 argmin 6.8 / 6.3; but 512 MB x 128: 6.05 / 6.3 and 128 MB: 4.7 / 4.9 - the ring
+  // takes longer to fill and to drain. B2R_ROW_TMA=1 forces it wherever it fits, 2 turns it off.
   if constexpr (V16 > 1) {
     const size_t row_bytes = size_t(row_len) * sizeof(InT);
-    if (tuning().row_tma == 1 && vec_ok && !chunks && ld == row_len && n_rows >= 16384 && sizeof(OutT) <= 8) {
-      constexpr int UT   = 4;  // rows per group at a time: shared-memory latency needs less unrolling
-      const int64_t unit = int64_t(kTmaConsumers / 32) * UT * gpw;  // rows of one batch per consumer warp
+    const int ring_mode    = tuning().row_tma;
+    const bool fits        = vec_ok && !chunks && ld == row_len && nvec <= G * cpl && sizeof(OutT) <= 8;
+    const bool wanted      = ring_mode == 1 ? n_rows >= 4096
+                                            : (ring_mode != 2 && nvec == G * cpl && nvec >= tuning().row_ring_min_vec &&
+                                          nvec <= tuning().row_ring_max_vec &&
+                                          size_t(n_rows) * row_bytes >= (size_t(tuning().row_ring_min_mb) << 20));
+    if (fits && wanted) {
+      const int64_t unit = int64_t(kTmaConsumers / 32) * (U / cpl) * gpw;  // rows of one pass of the 8 consumer warps
       int64_t k          = int64_t((size_t(tuning().row_tma_tile_kb) << 10) / (size_t(unit) * row_bytes));
       if (k < 1) k = 1;
       const int64_t tile_rows = unit * k;
-      const int stages        = tuning().row_tma_stages;
+      // a stage must always be used by the same team of consumers (a team that skips tiles could otherwise
+      // wait for a phase of a barrier two phases ahead of it): a multiple of the team count
+      int stages              = tuning().row_tma_stages / kRingTeams * kRingTeams;
+      if (stages < kRingTeams) stages = kRingTeams;
       const size_t smem       = size_t(stages) * ((size_t(tile_rows) * row_bytes + 127) / 128 * 128);
       if (smem <= (size_t(220) << 10)) {
-        auto kern      = row_reduce_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, UT, StoreT>;
-        cudaError_t ea = ensure_dynamic_smem(kern, size_t(smem));
-        if (ea != cudaSuccess) return ea;
-        int64_t ctas = int64_t(sm_count()) * resident_ctas(kern, kTmaThreads, smem);
+        int64_t ctas = sm_count();
         int64_t rpc  = ceil_div<int64_t>(n_rows, ctas);
         rpc          = ceil_div<int64_t>(rpc, tile_rows) * tile_rows;
         ctas         = ceil_div<int64_t>(n_rows, rpc);
-        kern<<<unsigned(ctas), kTmaThreads, smem, stream>>>(out, data, n_rows, int(row_len), init, inplace, main_op,
-                                                           reduce_op, final_op, G, int(tile_rows), rpc, stages,
-                                                           nullptr);
+#define B2R_LAUNCH_RING(U_, CPL_)                                                                              \
+  do {                                                                                                         \
+    auto kern      = row_reduce_ring_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, U_, CPL_, kRingTeams, StoreT>; \
+    cudaError_t ea = ensure_dynamic_smem(kern, smem);                                                          \
+    if (ea != cudaSuccess) return ea;                                                                          \
+    kern<<<unsigned(ctas), kRingTeams * kTmaConsumers + 32, smem, stream>>>(                                   \
+      out, data, n_rows, int(row_len), init, inplace, main_op, reduce_op, final_op, G, int(tile_rows), rpc,    \
+      stages, nullptr);                                                                                        \
+  } while (0)
+        if (cpl == 4) {
+          B2R_LAUNCH_RING(U / 4, 4);
+        } else if (cpl == 2) {
+          B2R_LAUNCH_RING(U / 2, 2);
+        } else {
+          B2R_LAUNCH_RING(U, 1);
+        }
+#undef B2R_LAUNCH_RING
         return cudaGetLastError();
       }
     }

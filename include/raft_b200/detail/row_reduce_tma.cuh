@@ -1,14 +1,25 @@
-// Row reduction of SHORT contiguous rows with TMA-staged shared-memory tiles.
+// Row reduction of SHORT contiguous rows out of a ring of shared-memory tiles.
 //
-// Rows of a contiguous row-major matrix (ld == row length) that are at most 2 KB long are
-// reduced by sub-warps exactly as in row_reduce_kernel<kRows> - G lanes per row, U rows per
-// group at a time, transposing sub-warp reduction, packed store - but the rows come out of a
-// ring of shared-memory tiles that one producer thread fills with bulk asynchronous copies
-// (cp.async.bulk + mbarrier), T consecutive rows = one contiguous block per copy. The bytes in
-// flight per SM are then (stages x tile) regardless of register pressure, and the consumer warps
-// spend no instruction on global addressing or on waiting for a global load.
+// Rows of a contiguous row-major matrix (ld == row length) of up to 32 x CPL 16-byte vectors are
+// reduced by sub-warps exactly as in row_reduce_kernel<kRows> - G lanes per row, CPL chunks of a
+// row per lane, U rows per group at a time (U x CPL = 8 shared-memory loads in flight per lane),
+// transposing sub-warp reduction, packed store - but the rows come out of a ring of shared-memory
+// tiles that one producer thread fills with bulk asynchronous copies (cp.async.bulk + mbarrier),
+// T consecutive rows = one contiguous block per copy. One CTA per SM owns a contiguous range of rows.
+//
+// Why a second kernel for rows the direct kernel can read: with short rows the work per row besides
+// the loads (set-up, the sub-warp reduction, the store) is a large share of a warp's time, and in
+// the direct kernel no new load is issued while a warp does that work. Here the producer keeps
+// STAGES x tile bytes in flight whatever the consumers do. Measured on 8,388,608 x 64 fp32 row
+// argmin: 6.78 TB/s against 6.3-6.5 for the direct kernel. What matters (same measurement):
+// tiles of 32 KB (16 KB tiles: 4.8 TB/s - twice the barrier traffic per byte), 4 stages (2: 4.6,
+// 6: 6.55 TB/s), one CTA per SM, a consumer team that takes a tile in ONE pass of its 8 warps, and
+// two such teams: with 8 consumer warps per SM the kernel is bound by what those warps can issue
+// (24 warp-instructions per row of 64 floats, 1.45 per clock: 5.1 TB/s).
+//
 // All mbarrier waits are bounded (see col_reduce_tma.cuh); a CTA whose wait runs out stops,
-// drains its copies in flight and writes NaN to the floating-point outputs it did not finish.
+// drains its copies in flight, marks `status` and writes NaN to the floating-point outputs it did
+// not finish.
 #pragma once
 
 #include "col_reduce_tma.cuh"
@@ -16,6 +27,8 @@
 
 namespace raft_b200 {
 namespace detail {
+
+constexpr int kRingTeams = 2;  // teams of 8 consumer warps per CTA of the ring kernel
 
 template <typename InT,
           typename OutT,
@@ -25,33 +38,36 @@ template <typename InT,
           typename FinalOp,
           int VEC,
           int U,
+          int CPL,
+          int TEAMS,
           typename StoreT = OutT>
-__global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* __restrict__ out,
-                                                                       const InT* __restrict__ data,
-                                                                       int64_t n_rows,
-                                                                       int row_len,
-                                                                       OutT init,
-                                                                       bool inplace,
-                                                                       MainOp main_op,
-                                                                       ReduceOp reduce_op,
-                                                                       FinalOp final_op,
-                                                                       int G,
-                                                                       int tile_rows,
-                                                                       int64_t rows_per_cta,
-                                                                       int STAGES,
-                                                                       int* __restrict__ status)
+__global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring_kernel(StoreT* __restrict__ out,
+                                                                        const InT* __restrict__ data,
+                                                                        int64_t n_rows,
+                                                                        int row_len,
+                                                                        OutT init,
+                                                                        bool inplace,
+                                                                        MainOp main_op,
+                                                                        ReduceOp reduce_op,
+                                                                        FinalOp final_op,
+                                                                        int G,
+                                                                        int tile_rows,
+                                                                        int64_t rows_per_cta,
+                                                                        int STAGES,
+                                                                        int* __restrict__ status)
 {
   using State          = typename state_for<OutT, ReduceOp>::type;
+  using Vec            = VecOf<InT, VEC>;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
   extern __shared__ __align__(128) unsigned char smem_tma[];
   __shared__ __align__(8) uint64_t s_full[kTmaMaxStages];
   __shared__ __align__(8) uint64_t s_empty[kTmaMaxStages];
   __shared__ int s_abort;
 
-  const size_t row_bytes    = size_t(row_len) * sizeof(InT);
+  const unsigned row_bytes  = unsigned(row_len) * unsigned(sizeof(InT));
   const size_t stage_stride = (size_t(tile_rows) * row_bytes + 127) / 128 * 128;
   const int tid             = threadIdx.x;
-  const bool producer       = tid >= kTmaConsumers;
+  const bool producer       = tid >= TEAMS * kTmaConsumers;
   const int64_t r_beg       = int64_t(blockIdx.x) * rows_per_cta;
   int64_t r_end             = r_beg + rows_per_cta;
   r_end                     = r_end < n_rows ? r_end : n_rows;
@@ -70,7 +86,7 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* 
   volatile int* abort_flag = &s_abort;
 
   if (producer) {
-    if (tid == kTmaConsumers) {
+    if (tid == TEAMS * kTmaConsumers) {
       int issued = 0;
       for (int t = 0; t < n_tiles; ++t) {
         const int s          = t % STAGES;
@@ -96,8 +112,14 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* 
     return;
   }
 
+  // TEAMS teams of 8 consumer warps take the tiles in turn (a team owns a whole tile): with short rows the
+  // consumers are bound by instruction issue, and a second team doubles what an SM can issue for them.
+  // STAGES must be a multiple of TEAMS, so that a stage is always served by the same team: a waiter may be
+  // at most one phase behind its barrier, and a team that skips tiles would get two phases ahead of a stage
+  // it shares with a slower team.
   const int lane = tid & 31;
-  const int warp = tid >> 5;
+  const int warp = (tid >> 5) & (kTmaConsumers / 32 - 1);
+  const int team = tid / kTmaConsumers;
   const int lg   = 31 - __clz(G);
   const int lig  = lane & (G - 1);
   const int grp  = lane >> lg;
@@ -105,10 +127,12 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* 
   const int gpw  = 1 << gsh;
   const int nvec = row_len / VEC;
   const int rows_per_batch = U * gpw;
+  const bool exact         = nvec == G * CPL;  // every lane of a group holds CPL whole chunks
   const SubwarpLayout lay  = subwarp_layout<U>(lig, G);
+  const unsigned step_full = unsigned(gpw) * row_bytes;
 
-  int t = 0;
-  for (; t < n_tiles; ++t) {
+  int t = team;
+  for (; t < n_tiles; t += TEAMS) {
     const int s          = t % STAGES;
     const unsigned phase = (t / STAGES) & 1u;
     if (!mbar_wait_bounded(&s_full[s], phase, abort_flag)) break;
@@ -117,28 +141,57 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* 
     const unsigned char* tile = smem_tma + s * stage_stride;
     const int n_batches       = (nr + rows_per_batch - 1) / rows_per_batch;
     for (int b = warp; b < n_batches; b += kTmaConsumers / 32) {
-      const int lrow0 = b * rows_per_batch + grp;  // slot u -> tile row lrow0 + u*gpw
+      const int lrow0 = b * rows_per_batch + grp;  // slot u -> tile row lrow0 + u * gpw
       const int left  = nr - lrow0;
       const int slots = (left + gpw - 1) >> gsh;
       const int valid = left <= 0 ? 0 : (slots < U ? slots : U);
-      const unsigned char* base = tile + size_t(valid > 0 ? lrow0 : nr - 1) * row_bytes;
-      const size_t step         = valid > 0 ? size_t(gpw) * row_bytes : 0;
       State st[U];
 #pragma unroll
       for (int u = 0; u < U; ++u)
         init_state<OutT, State, isSum>(st[u], init, lig == 0);
-      for (int c = lig; c < nvec; c += G) {
-        VecOf<InT, VEC> v[U];
+      Vec v[U][CPL];
+      if (valid == U && exact) {
+        const unsigned char* base = tile + unsigned(lrow0) * row_bytes + unsigned(lig) * unsigned(sizeof(Vec));
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const int uu = u < valid ? u : (valid > 0 ? valid - 1 : 0);
-          v[u] = *reinterpret_cast<const VecOf<InT, VEC>*>(base + uu * step + size_t(c) * VEC * sizeof(InT));
+#pragma unroll
+          for (int k = 0; k < CPL; ++k)
+            v[u][k] = *reinterpret_cast<const Vec*>(base + u * step_full + unsigned(k * G) * unsigned(sizeof(Vec)));
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e)
-            push_element<OutT, IdxT>(st[u], v[u].e[e], c * VEC + e, main_op, reduce_op);
+          for (int k = 0; k < CPL; ++k) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              push_element<OutT, IdxT>(st[u], v[u][k].e[e], (lig + k * G) * VEC + e, main_op, reduce_op);
+          }
+        }
+      } else {
+        // ragged batch (fewer than U real rows in the tile) or a row length below G x CPL chunks:
+        // slots and chunks that do not exist re-read one that does and are ignored
+        const unsigned char* base = tile + unsigned(valid > 0 ? lrow0 : nr - 1) * row_bytes;
+        const unsigned step       = valid > 0 ? step_full : 0u;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int uu = u < valid ? u : (valid > 0 ? valid - 1 : 0);
+#pragma unroll
+          for (int k = 0; k < CPL; ++k) {
+            const int c  = lig + k * G;
+            const int cc = c < nvec ? c : 0;
+            v[u][k]      = *reinterpret_cast<const Vec*>(base + uu * step + unsigned(cc) * unsigned(sizeof(Vec)));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int k = 0; k < CPL; ++k) {
+            if (lig + k * G < nvec) {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e)
+                push_element<OutT, IdxT>(st[u], v[u][k].e[e], (lig + k * G) * VEC + e, main_op, reduce_op);
+            }
+          }
         }
       }
       subwarp_transpose_reduce<U>(st, lig, G, reduce_op);
@@ -146,15 +199,15 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* 
 #pragma unroll
         for (int i = 0; i < U; ++i) {
           if (i < lay.n_final) {
-            const int slot  = lay.prefix * lay.n_final + i;
-            const int lr    = lrow0 + slot * gpw;
+            const int slot = lay.prefix * lay.n_final + i;
+            const int lr   = lrow0 + slot * gpw;
             if (lr < nr) {
               const int64_t r = tile_row0 + lr;
-              OutT v          = st[i].value();
+              OutT val        = st[i].value();
               if constexpr (std::is_same<StoreT, OutT>::value) {
-                if (inplace) v = reduce_op(out[r], v);
+                if (inplace) val = reduce_op(out[r], val);
               }
-              out[r] = final_op(v);
+              out[r] = final_op(val);
             }
           }
         }
@@ -164,9 +217,9 @@ __global__ void __launch_bounds__(kTmaThreads, 4) row_reduce_tma_kernel(StoreT* 
     if (lane == 0) mbar_arrive(&s_empty[s]);
   }
   if (t < n_tiles) {
-    // a bounded wait ran out: make it visible - the rows this warp did not finish become NaN
+    // a bounded wait ran out: make it visible - the rows this CTA did not finish become NaN
     if constexpr (std::is_floating_point<StoreT>::value) {
-      for (int64_t r = r_beg + int64_t(t) * tile_rows + tid; r < r_end; r += kTmaConsumers)
+      for (int64_t r = r_beg + int64_t(t) * tile_rows + (tid & (kTmaConsumers - 1)); r < r_end; r += kTmaConsumers)
         out[r] = StoreT(NAN);
     }
   }
