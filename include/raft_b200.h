@@ -250,13 +250,15 @@ B2R_API int b2r_matrix_argmax(void* out,
  * a 1 MiB array inside the library image (present on every GPU that loads the library, for
  * the life of the process); the call uses no cudaMalloc, cudaFree, cudaMallocAsync or any
  * other allocating routine.
- *  - The call needs (row ranges) x n_cols x 8 bytes of that array, where the number of row
- *    ranges is the CTAs of one resident wave divided by the column tiles (128 columns each).
- *    With the default launch shape on a 148-SM B200 that is at most 0.6 MiB for any n_rows and
- *    n_cols, so every shape is accepted; a need above 1 MiB (a wider launch shape through
- *    B2R_COL_CPS, a GPU with more SMs) returns B2R_ERR_TOO_LARGE and launches nothing.
- *    b2r_column_sum_f32_noalloc_max_scratch() returns the limit, b2r_reduce_workspace_bytes()
- *    the need of a shape.
+ *  - The call needs one fp64 partial row (n_cols x 8 bytes) per row range of the launch, plus a
+ *    status word per CTA for the TMA-staged kernel. The launch shape is planned UNDER the array's
+ *    size: where the preferred shape would need more (148 CTAs x n_cols x 8 bytes for n_cols near
+ *    1024; two row ranges of more than 65536 columns) the call uses fewer CTAs or row ranges, down
+ *    to a single row range, which needs no scratch at all - so every n_rows x n_cols is accepted
+ *    on today's GPUs, a few of them on fewer CTAs than b2r_reduce would use (its result then
+ *    differs from b2r_reduce's in the last bits: another summation order). Should a plan ever not
+ *    fit, the call returns B2R_ERR_TOO_LARGE and launches nothing.
+ *    b2r_column_sum_f32_noalloc_max_scratch() returns the size of the array.
  *  - The first call on each device looks up the array's device address; make that first call
  *    before any stream capture begins on that device.
  *  - All calls on a device share the one array. Its contents are fully rewritten by each call
@@ -304,6 +306,15 @@ B2R_API int b2r_synth_fill(void* dst,
                            double lo,
                            double hi,
                            b2r_stream_t stream);
+
+/*
+ * Measurement aids (no counterpart in the reference, whose benchmarks report times without a
+ * floor): an empty kernel - what a pair of events around any launch costs - and a kernel that
+ * only reads `bytes` bytes at `data` (16-byte aligned) once, every SM streaming, which is the
+ * fastest any kernel of this library could consume them. `sink` may be NULL.
+ */
+B2R_API int b2r_probe_empty_launch(b2r_stream_t stream);
+B2R_API int b2r_probe_stream_read(const void* data, size_t bytes, float* sink, b2r_stream_t stream);
 
 /*
  * Scratch the library allocates for itself (calls made with workspace == NULL) comes from a

@@ -666,10 +666,17 @@ struct ColPlan {
   int64_t rows_per_cta;
   size_t smem;
   size_t scratch;
+  // the register-staged plan, kept beside a tiled-TMA plan in case the tensor map cannot be made
+  unsigned reg_grid_x;
+  unsigned reg_grid_y;
+  int64_t reg_rows_per_cta;
+  size_t reg_smem;
 };
 
+// `scratch_cap` (0: none) bounds the scratch the plan may ask for: a caller with a fixed scratch area gets
+// fewer row ranges / CTAs (down to a single row range, which needs no scratch at all) instead of a refusal.
 template <typename InT, typename OutT, typename State>
-inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, int64_t ld)
+inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, int64_t ld, size_t scratch_cap = 0)
 {
   constexpr int TPB = 256;
   constexpr int U   = 8;
@@ -687,6 +694,9 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
   const int64_t max_gy = ceil_div<int64_t>(n_rows, int64_t(p.TY) * U);  // >= one full unrolled step each
   if (gy > max_gy) gy = max_gy;
   if (gy > 65535) gy = 65535;
+  const size_t part_row = size_t(n_cols) * sizeof(typename State::carry_t);  // one partial row
+  if (scratch_cap > 0 && gy > 1 && align_up(size_t(gy) * part_row, 256) > scratch_cap)
+    gy = int64_t((scratch_cap - 255) / part_row);
   if (gy < 1) gy = 1;
   int64_t rpc     = ceil_div<int64_t>(n_rows, gy);
   rpc             = ceil_div<int64_t>(rpc, p.TY) * p.TY;
@@ -701,32 +711,45 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
   p.stages       = 0;
   p.tile_rows    = 0;
   p.off_status   = 0;
+  p.reg_grid_x   = p.grid_x;
+  p.reg_grid_y   = p.grid_y;
+  p.reg_rows_per_cta = rpc;
+  p.reg_smem     = p.smem;
   // TMA-staged variant: rows contiguous, the whole width in one CTA, enough rows to stream
   const size_t row_bytes = size_t(n_cols) * sizeof(InT);
   if (tuning().col_tma == 1 && vec_ok && ld == n_cols && ncv <= kTmaConsumers && row_bytes % 16 == 0 &&
       n_rows >= 8192) {
     unsigned txp = next_pow2(unsigned(ncv));
-    p.TX         = int(txp);
-    p.TY         = kTmaConsumers / p.TX;
+    const int ty = kTmaConsumers / int(txp);
     size_t tile  = size_t(tuning().col_tma_tile_kb) << 10;
-    int64_t tr   = int64_t(tile / row_bytes) / p.TY * p.TY;
-    if (tr < p.TY) tr = p.TY;
-    p.tile_rows  = int(tr);
+    int64_t tr   = int64_t(tile / row_bytes) / ty * ty;
+    if (tr < ty) tr = ty;
     int64_t ctas = sm_count();
-    int64_t rpc2 = ceil_div<int64_t>(n_rows, ctas);
-    rpc2         = ceil_div<int64_t>(rpc2, tr) * tr;
-    ctas         = ceil_div<int64_t>(n_rows, rpc2);
-    p.grid_x     = unsigned(ctas);
-    p.grid_y     = 1;
-    p.rows_per_cta = rpc2;
+    // a partial row and a status word per CTA: fewer CTAs when the caller's scratch is bounded
+    if (scratch_cap > 0 && align_up(size_t(ctas) * part_row, 256) + align_up(size_t(ctas) * sizeof(int), 256) > scratch_cap)
+      ctas = scratch_cap > 1024 ? int64_t((scratch_cap - 1024) / (part_row + sizeof(int))) : 0;
     const size_t stage = (size_t(tr) * row_bytes + 127) / 128 * 128;
-    p.stages     = tuning().tma_stages;
-    p.smem       = size_t(p.stages) * stage + size_t(kTmaConsumers) * p.vec * sizeof(State);
-    const size_t parts = align_up(size_t(ctas) * size_t(n_cols) * sizeof(typename State::carry_t), 256);
-    p.off_status = parts;
-    const size_t need = parts + align_up(size_t(ctas) * sizeof(int), 256);
-    p.scratch    = p.scratch > need ? p.scratch : need;
-    p.tma        = ctas > 1 && p.smem <= (size_t(220) << 10);
+    const size_t smem  = size_t(tuning().tma_stages) * stage + size_t(kTmaConsumers) * p.vec * sizeof(State);
+    // (a quarter of the SMs and fewer: the register-staged plan above, with its four CTAs per SM, is the better one)
+    if (ctas * 4 >= sm_count() && smem <= (size_t(220) << 10)) {
+      int64_t rpc2 = ceil_div<int64_t>(n_rows, ctas);
+      rpc2         = ceil_div<int64_t>(rpc2, tr) * tr;
+      ctas         = ceil_div<int64_t>(n_rows, rpc2);
+      if (ctas > 1) {
+        p.TX           = int(txp);
+        p.TY           = kTmaConsumers / p.TX;
+        p.tile_rows    = int(tr);
+        p.grid_x       = unsigned(ctas);
+        p.grid_y       = 1;
+        p.rows_per_cta = rpc2;
+        p.stages       = tuning().tma_stages;
+        p.smem         = smem;
+        const size_t parts = align_up(size_t(ctas) * part_row, 256);
+        p.off_status   = parts;
+        p.scratch      = parts + align_up(size_t(ctas) * sizeof(int), 256);
+        p.tma          = true;
+      }
+    }
   }
   // tiled-TMA variant: wide matrices (more than one 32-vector column block), 16-byte aligned rows,
   // and enough data that filling the rings pays (measured: on par with the register-staged kernel
@@ -743,6 +766,8 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
       // at most four CTAs per SM in all, like the register-staged kernel: the partial rows stay
       // within a few hundred KB whatever the shape
       for (int64_t gy = 2; gy <= max_gy && gx * gy <= int64_t(4) * sms; ++gy) {
+        if (scratch_cap > 0 && align_up(size_t(gy) * part_row, 256) + align_up(size_t(gy) * sizeof(int), 256) > scratch_cap)
+          break;  // a partial row and a status word per row range must fit the caller's scratch
         int64_t rpc         = ceil_div<int64_t>(ceil_div<int64_t>(n_rows, gy), kBoxRows) * kBoxRows;
         const int64_t gy_r  = ceil_div<int64_t>(n_rows, rpc);
         const int64_t waves = ceil_div<int64_t>(gx * gy_r, sms);
@@ -753,17 +778,23 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
         }
       }
       if (best_gy >= 2) {
-        int64_t rpc    = ceil_div<int64_t>(ceil_div<int64_t>(n_rows, best_gy), kBoxRows) * kBoxRows;
-        p.grid_x       = unsigned(gx);
-        p.grid_y       = unsigned(ceil_div<int64_t>(n_rows, rpc));
-        p.rows_per_cta = rpc;
-        p.stages       = 4;
-        p.smem         = size_t(p.stages) * size_t(kBoxRows) * size_t(BX) * sizeof(InT) +
-                 size_t(kTmaConsumers / 32) * size_t(BX) * sizeof(State);
-        const size_t parts = align_up(size_t(p.grid_y) * size_t(n_cols) * sizeof(typename State::carry_t), 256);
-        p.off_status       = parts;
-        p.scratch          = parts + align_up(size_t(p.grid_y) * sizeof(int), 256);
-        p.tma2d            = p.grid_y >= 2 && p.smem <= (size_t(220) << 10);
+        const int64_t rpc2   = ceil_div<int64_t>(ceil_div<int64_t>(n_rows, best_gy), kBoxRows) * kBoxRows;
+        const unsigned gy2   = unsigned(ceil_div<int64_t>(n_rows, rpc2));
+        const size_t smem2   = size_t(4) * size_t(kBoxRows) * size_t(BX) * sizeof(InT) +
+                             size_t(kTmaConsumers / 32) * size_t(BX) * sizeof(State);
+        if (gy2 >= 2 && smem2 <= (size_t(220) << 10)) {
+          p.grid_x       = unsigned(gx);
+          p.grid_y       = gy2;
+          p.rows_per_cta = rpc2;
+          p.stages       = 4;
+          p.smem         = smem2;
+          const size_t parts = align_up(size_t(gy2) * part_row, 256);
+          p.off_status   = parts;
+          // (the register-staged plan's partial rows fit too: it is the fallback of this one)
+          const size_t need = parts + align_up(size_t(gy2) * sizeof(int), 256);
+          p.scratch      = need > p.scratch ? need : p.scratch;
+          p.tma2d        = true;
+        }
       }
     }
   }
@@ -771,11 +802,11 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
 }
 
 template <typename InT, typename OutT, typename ReduceOp>
-inline size_t col_reduce_scratch_bytes(const InT* data, int64_t n_rows, int64_t n_cols, int64_t ld)
+inline size_t col_reduce_scratch_bytes(const InT* data, int64_t n_rows, int64_t n_cols, int64_t ld, size_t scratch_cap = 0)
 {
   using State = typename state_for<OutT, ReduceOp>::type;
   if (n_rows <= 0 || n_cols <= 0) return 0;
-  return plan_col_reduce<InT, OutT, State>(data, n_rows, n_cols, ld).scratch;
+  return plan_col_reduce<InT, OutT, State>(data, n_rows, n_cols, ld, scratch_cap).scratch;
 }
 
 template <typename InT,
@@ -795,7 +826,8 @@ cudaError_t launch_col_reduce(OutT* out,
                               ReduceOp reduce_op,
                               FinalOp final_op,
                               cudaStream_t stream,
-                              Workspace ws = Workspace{})
+                              Workspace ws = Workspace{},
+                              size_t scratch_cap = 0)
 {
   constexpr int TPB = 256;
   constexpr int U   = 8;
@@ -804,7 +836,7 @@ cudaError_t launch_col_reduce(OutT* out,
   if (n_cols <= 0) return cudaSuccess;
   if (n_rows < 0) n_rows = 0;
 
-  const ColPlan p = plan_col_reduce<InT, OutT, State>(data, n_rows > 0 ? n_rows : 1, n_cols, ld);
+  ColPlan p = plan_col_reduce<InT, OutT, State>(data, n_rows > 0 ? n_rows : 1, n_cols, ld, scratch_cap);
   Scratch scratch(ws, p.scratch, stream);
   if (scratch.error() != cudaSuccess) return scratch.error();
   using CarryT    = typename State::carry_t;
@@ -847,8 +879,12 @@ cudaError_t launch_col_reduce(OutT* out,
           out, partial, int(p.grid_y), n_cols, init, inplace, reduce_op, final_op, cta_status);
         return cudaGetLastError();
       }
-      // no tensor map (driver entry point missing): the register-staged kernel below uses the same
-      // scratch layout [row ranges][n_cols]
+      // no tensor map (driver entry point missing): the register-staged plan, whose partial rows
+      // [row ranges][n_cols] fit the same scratch
+      p.grid_x       = p.reg_grid_x;
+      p.grid_y       = p.reg_grid_y;
+      p.rows_per_cta = p.reg_rows_per_cta;
+      p.smem         = p.reg_smem;
     }
   }
   const dim3 grid(p.grid_x, p.grid_y);

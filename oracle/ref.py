@@ -7,11 +7,35 @@ import os
 
 import torch
 
-from raft_b200 import _lib as L
-
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_ref", "libraft_ref.so")
 _lib = None
+
+
+class _Abi:
+    """The enums and the descriptor the wrapper shares with the product's C ABI (include/raft_b200.h),
+    restated here so that this module - and the benchmark's reference arm - never imports the product."""
+    F32, F64, F16, I32, I64, I16, U32 = 0, 1, 2, 3, 4, 5, 6
+    KVP_I32_F32, KVP_I32_F64, KVP_I32_I16, KVP_I32_I32 = 16, 17, 18, 19
+    ROW_MAJOR, COL_MAJOR = 0, 1
+    ALONG_ROWS, ALONG_COLUMNS = 0, 1
+    MAIN_IDENTITY, MAIN_SQ, MAIN_ABS, MAIN_NZ, MAIN_TO_KVP = 0, 1, 2, 3, 4
+    REDUCE_ADD, REDUCE_MIN, REDUCE_MAX, REDUCE_ARGMIN, REDUCE_ARGMAX = 0, 1, 2, 3, 4
+    FINAL_IDENTITY, FINAL_SQRT, FINAL_MUL_CONST, FINAL_DIV_CONST, FINAL_ABS = 0, 1, 2, 3, 4
+
+    class ReduceDesc(ctypes.Structure):
+        _fields_ = [("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32), ("layout", ctypes.c_int32),
+                    ("apply", ctypes.c_int32), ("n_rows", ctypes.c_int64), ("n_cols", ctypes.c_int64),
+                    ("main_op", ctypes.c_int32), ("reduce_op", ctypes.c_int32), ("final_op", ctypes.c_int32),
+                    ("inplace", ctypes.c_int32), ("init", ctypes.c_double), ("init_i", ctypes.c_int64),
+                    ("init_key", ctypes.c_int64), ("final_scalar", ctypes.c_double)]
+
+
+L = _Abi
+_DTYPES = {torch.float32: L.F32, torch.float64: L.F64, torch.float16: L.F16, torch.int32: L.I32,
+           torch.int64: L.I64, torch.int16: L.I16}
+_KVP_OF = {L.F32: L.KVP_I32_F32, L.F64: L.KVP_I32_F64, L.I16: L.KVP_I32_I16, L.I32: L.KVP_I32_I32}
+_NORM = {"L1": 1, "L2": 2, "Linf": 3}
 
 
 def available():
@@ -39,14 +63,17 @@ def _stream(dev):
 
 
 def reduce(data, apply, dots, layout=L.ROW_MAJOR, main_op=L.MAIN_IDENTITY, reduce_op=L.REDUCE_ADD,
-           final_op=L.FINAL_IDENTITY, final_scalar=1.0, init=0.0, init_key=0, inplace=False, out_dtype=None):
+           final_op=L.FINAL_IDENTITY, final_scalar=1.0, init=0.0, init_key=0, inplace=False, out_dtype=None,
+           kvp=None):
     """Runs the reference's raft::linalg::reduce. `data` is the logical [n_rows, n_cols] tensor
-    (row- or column-major memory per `layout`); `dots` a tensor or a linalg.KeyValueVector.
-    Returns the library status (0 ok, 2 combination not built into the wrapper)."""
-    from raft_b200.linalg import _DTYPES, _KVP_OF, KeyValueVector
+    (row- or column-major memory per `layout`); `dots` a tensor, or for key/value output anything
+    with a data_ptr() over an array of {int32 key, value} pairs (a linalg.KeyValueVector; with
+    kvp=True a plain tensor of that many bytes). Returns the library status (0 ok, 2 combination
+    not built into the wrapper)."""
     n_rows, n_cols = data.shape
     in_dt = _DTYPES[data.dtype]
-    kvp = isinstance(dots, KeyValueVector)
+    if kvp is None:
+        kvp = not isinstance(dots, torch.Tensor)
     out_dt = _KVP_OF[in_dt] if kvp else _DTYPES[dots.dtype]
     desc = L.ReduceDesc(in_dtype=in_dt, out_dtype=out_dt, layout=layout, apply=apply, n_rows=n_rows, n_cols=n_cols,
                         main_op=main_op, reduce_op=reduce_op, final_op=final_op, inplace=1 if inplace else 0,
@@ -59,7 +86,6 @@ def reduce(data, apply, dots, layout=L.ROW_MAJOR, main_op=L.MAIN_IDENTITY, reduc
 
 
 def rows_by_key(sums, A, keys, nkeys, weights=None, reset=True):
-    from raft_b200.linalg import _DTYPES
     nrows, ncols = A.shape
     with torch.cuda.device(A.device):
         return load().ref_rows_by_key(sums.data_ptr(), A.data_ptr(), A.stride(0), keys.data_ptr(),
@@ -68,7 +94,6 @@ def rows_by_key(sums, A, keys, nkeys, weights=None, reset=True):
 
 
 def cols_by_key(out, data, keys, nkeys, reset=True):
-    from raft_b200.linalg import _DTYPES
     nrows, ncols = data.shape
     with torch.cuda.device(data.device):
         return load().ref_cols_by_key(out.data_ptr(), data.data_ptr(), keys.data_ptr(), _DTYPES[data.dtype], nrows,
@@ -77,7 +102,6 @@ def cols_by_key(out, data, keys, nkeys, reset=True):
 
 def row_normalize(out, data, norm_type):
     """The reference's raft::linalg::row_normalize<norm_type> (default eps). norm_type: "L1", "L2", "Linf"."""
-    from raft_b200.linalg import _DTYPES, _NORM
     n_rows, n_cols = data.shape
     with torch.cuda.device(data.device):
         return load().ref_row_normalize(out.data_ptr(), data.data_ptr(), _DTYPES[data.dtype], n_rows, n_cols,
@@ -86,7 +110,6 @@ def row_normalize(out, data, norm_type):
 
 def map_then_sum_reduce(out, data):
     """The reference's mapThenSumReduce(out, len, identity_op, stream, data)."""
-    from raft_b200.linalg import _DTYPES
     with torch.cuda.device(data.device):
         return load().ref_map_then_sum_reduce(out.data_ptr(), data.data_ptr(), _DTYPES[data.dtype], data.numel(),
                                               _stream(data.device))

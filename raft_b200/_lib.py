@@ -62,6 +62,8 @@ SIGNATURES = {
     "b2r_column_sum_f32_noalloc_max_scratch": (_sz, []),
     "b2r_apply_final": (ctypes.c_int, [_vp, _i32, _i64, _i32, _dbl, _vp]),
     "b2r_synth_fill": (ctypes.c_int, [_vp, _i32, _i64, _i64, _u64, _i32, _dbl, _dbl, _vp]),
+    "b2r_probe_empty_launch": (ctypes.c_int, [_vp]),
+    "b2r_probe_stream_read": (ctypes.c_int, [_vp, _sz, _vp, _vp]),
     "b2r_trim_scratch_pool": (ctypes.c_int, []),
     "b2r_reload_tuning": (ctypes.c_int, []),
     "b2r_status_string": (ctypes.c_char_p, [ctypes.c_int]),

@@ -59,8 +59,12 @@ extern "C" int b2r_column_sum_f32_noalloc(float* out, const float* in, int64_t n
   if (n_rows > 0 && n_cols > 0 && in == nullptr) return B2R_ERR_BAD_ARG;
   if (final_op < B2R_FINAL_IDENTITY || final_op > B2R_FINAL_ABS) return B2R_ERR_BAD_ARG;
   if (n_cols == 0) return B2R_OK;
-  // the partial rows this shape needs must fit the fixed array: refuse, never allocate
-  const size_t need = detail::col_reduce_scratch_bytes<float, float, op::Add>(in, n_rows, n_cols, n_cols);
+  // The launch shape is planned under the array's size: shapes whose preferred plan would need more
+  // (a partial row per CTA of 148 x n_cols x 8 bytes for n_cols near 1024, two row ranges of more than
+  // 65536 columns) get fewer CTAs or a single row range, which needs no scratch at all. The check
+  // stays as the guard of the array: refuse, never allocate.
+  const size_t need = detail::col_reduce_scratch_bytes<float, float, op::Add>(in, n_rows, n_cols, n_cols,
+                                                                              kNoAllocScratchBytes);
   if (need > kNoAllocScratchBytes) return B2R_ERR_TOO_LARGE;
   void* scratch = nullptr;
   cudaError_t e = noalloc_scratch(&scratch);
@@ -70,7 +74,7 @@ extern "C" int b2r_column_sum_f32_noalloc(float* out, const float* in, int64_t n
   ws.bytes = kNoAllocScratchBytes;
   op::RuntimeFinal<float> fin{final_op, float(final_scalar)};
   e = detail::launch_col_reduce<float, float, int64_t>(out, in, n_rows, n_cols, n_cols, 0.0f, false, op::Identity{},
-                                                       op::Add{}, fin, to_stream(stream), ws);
+                                                       op::Add{}, fin, to_stream(stream), ws, kNoAllocScratchBytes);
   return set_cuda_error(e);
 }
 

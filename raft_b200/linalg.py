@@ -380,6 +380,20 @@ def row_normalize(data, norm_type="L2", out=None, eps=1e-8):
     return out
 
 
+def probe_empty_launch(device):
+    """One empty kernel on the device's current stream (the cost floor of an event pair around a launch)."""
+    with _on(device):
+        L.check(L.load().b2r_probe_empty_launch(_stream_ptr(device)), "b2r_probe_empty_launch")
+
+
+def probe_stream_read(data):
+    """Reads `data` once with plain streaming loads and does nothing else (the read floor of its size)."""
+    _require_cuda(data, "data")
+    with _on(data.device):
+        L.check(L.load().b2r_probe_stream_read(data.data_ptr(), data.numel() * data.element_size(), None,
+                                               _stream_ptr(data.device)), "b2r_probe_stream_read")
+
+
 def reload_tuning():
     """Makes the library read its B2R_* environment knobs again (they are otherwise read once, at the
     first call). For tests and sweeps that change them within one process."""

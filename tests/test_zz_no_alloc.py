@@ -43,19 +43,47 @@ def test_matches_regular_entry_point_twice_in_a_row(cuda, rows, cols):
     assert torch.equal(mean, linalg.reduce(a, linalg.ALONG_COLUMNS, final_op="div_const", final_scalar=float(rows)))
 
 
+def _free_bytes():
+    free, _ = torch.cuda.mem_get_info()
+    return free
+
+
+@pytest.mark.parametrize("rows,cols", [(100000, 1024), (20000, 1000), (300, 70000), (8192, 70000), (9000, 900)])
+def test_shapes_whose_preferred_plan_exceeds_the_array(cuda, rows, cols):
+    """b2r_reduce would use more than 1 MiB of scratch for these (a partial row per CTA of 148 x cols x 8
+    bytes, or two row ranges of 70000 columns); the entry point plans a launch that fits its array, runs
+    it twice in a row, takes no device memory, and agrees with b2r_reduce within the suite's tolerance."""
+    data = torch.empty((rows, cols), dtype=torch.float32, device=cuda)
+    linalg.synth_fill(data, 73, "uniform", -1, 1)
+    expect = linalg.reduce(data, linalg.ALONG_COLUMNS).cpu().numpy().astype(np.float64)
+    got = torch.full((cols,), float("nan"), dtype=torch.float32, device=cuda)
+    assert _noalloc(data, got) == L.OK  # first call on the device may resolve the array's address
+    torch.cuda.synchronize()
+    before = _free_bytes()
+    for _ in range(2):
+        got.fill_(float("nan"))
+        assert _noalloc(data, got) == L.OK
+        torch.cuda.synchronize()
+        g = got.cpu().numpy().astype(np.float64)
+        diff = np.abs(expect - g)
+        assert np.all((diff <= 1e-5) | (diff <= 1e-5 * np.maximum(np.abs(expect), np.abs(g))))
+    assert _free_bytes() == before  # nothing was allocated on the device
+
+
 def test_limit_and_bad_arguments(cuda, knobs):
     lib = L.load()
     assert lib.b2r_column_sum_f32_noalloc_max_scratch() == 1 << 20
-    # a launch shape four times wider than the default needs 2368 row ranges x 128 columns of
-    # fp64 partials = 2.4 MB: more than the fixed array, so the call is refused and nothing runs
+    # a launch shape four times wider than the default would need 2368 row ranges x 128 columns of fp64
+    # partials = 2.4 MB from b2r_reduce; the entry point fits its plan under the 1 MiB array instead
     tall = torch.ones((200000, 128), dtype=torch.float32, device=cuda)
     out = torch.full((128,), 5.0, dtype=torch.float32, device=cuda)
-    knobs(B2R_COL_CPS="16")
+    knobs(B2R_COL_CPS="16", B2R_COL_TMA="2")
     assert linalg.reduce_workspace_bytes(tall, linalg.ALONG_COLUMNS) > (1 << 20)
-    assert _noalloc(tall, out) == L.ERR_TOO_LARGE
+    assert _noalloc(tall, out) == L.OK
     torch.cuda.synchronize()
-    assert torch.all(out == 5.0)
-    knobs(B2R_COL_CPS=None)
+    assert torch.all(out == 200000.0)
+    knobs(B2R_COL_CPS=None, B2R_COL_TMA=None)
+    out.fill_(5.0)
     assert _noalloc(tall, out) == L.OK
     assert torch.all(out == 200000.0)
     small = torch.ones((8, 8), dtype=torch.float32, device=cuda)
