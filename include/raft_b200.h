@@ -42,7 +42,8 @@ typedef enum {
   B2R_ERR_BAD_ARG     = 1, /* null pointer, negative size, inconsistent descriptor           */
   B2R_ERR_UNSUPPORTED = 2, /* a dtype / operator combination the library was not built for   */
   B2R_ERR_CUDA        = 3, /* a CUDA runtime call failed, see b2r_last_cuda_error()          */
-  B2R_ERR_TOO_LARGE   = 4  /* a size beyond a stated limit of the entry point                */
+  B2R_ERR_TOO_LARGE   = 4, /* a size beyond a stated limit of the entry point                */
+  B2R_ERR_TIMEOUT     = 5  /* a bounded wait inside a kernel ran out (reported by the status queries) */
 } b2r_status;
 
 typedef enum {
@@ -306,6 +307,42 @@ B2R_API int b2r_synth_fill(void* dst,
                            double lo,
                            double hi,
                            b2r_stream_t stream);
+
+/*
+ * All-reduce (sum) of small per-GPU partials over peer memory, for the row-sharded column and by-key
+ * reductions: ONE kernel per GPU pushes its partial into every peer's exchange area with plain stores
+ * over NVLink, raises a flag, waits (bounded) for the peers' flags in its own memory, sums the slots in
+ * rank order and applies the deferred scale - in place of one library collective per tensor plus a
+ * final_op launch. The collective it stands for in the reference is comms_t::allreduce
+ * (cpp/include/raft/comms/detail/std_comms.hpp:366-375); the reference has no kernel of this kind.
+ *
+ *  b2r_peer_area_create      allocates this rank's exchange area on the current device (cudaMalloc, a
+ *                            set-up call): 2 x world slots of `max_payload_bytes` plus flags. HOST pointer out.
+ *  b2r_peer_area_ipc_handle  writes the 64-byte CUDA IPC handle of the area (to send to the other processes).
+ *  b2r_peer_area_open        maps the area of `peer_rank` (another process on this node) from its handle.
+ *  b2r_peer_area_link        the same for an area of another device of THIS process (enables peer access).
+ *  b2r_peer_allreduce_sum    sums[0..n_f32) and counts[0..n_i64) (device, either may be empty) become the
+ *                            sums over all ranks, fp32 sums multiplied by `scale`; asynchronous on `stream`.
+ *                            Every rank must make the same sequence of calls with the same sizes. A payload
+ *                            above the area's slot size returns B2R_ERR_TOO_LARGE.
+ *  b2r_peer_area_status      (synchronising, after the caller's own sync) B2R_ERR_TIMEOUT in *status_out if a
+ *                            wait of an earlier call ran out - that call left its outputs unfinished -, else
+ *                            B2R_OK; `clear` resets it. The limit is 2 s unless b2r_peer_area_set_wait_limit_ms.
+ */
+B2R_API int b2r_peer_area_create(int32_t world, int32_t rank, size_t max_payload_bytes, void** area_out);
+B2R_API int b2r_peer_area_ipc_handle(void* area, void* handle_out_64_bytes);
+B2R_API int b2r_peer_area_open(void* area, int32_t peer_rank, const void* handle_64_bytes);
+B2R_API int b2r_peer_area_link(void* area, int32_t peer_rank, void* peer_area_same_process);
+B2R_API int b2r_peer_area_set_wait_limit_ms(void* area, uint32_t ms);
+B2R_API int b2r_peer_allreduce_sum(void* area,
+                                   float* sums,
+                                   int64_t n_f32,
+                                   long long* counts,
+                                   int64_t n_i64,
+                                   double scale,
+                                   b2r_stream_t stream);
+B2R_API int b2r_peer_area_status(void* area, int32_t* status_out, int32_t clear);
+B2R_API int b2r_peer_area_destroy(void* area);
 
 /*
  * Measurement aids (no counterpart in the reference, whose benchmarks report times without a

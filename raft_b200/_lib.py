@@ -10,7 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libraft_b200.so")
 
 # b2r_status
-OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE = 0, 1, 2, 3, 4
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE, ERR_TIMEOUT = 0, 1, 2, 3, 4, 5
 # b2r_dtype
 F32, F64, F16, I32, I64, I16, U32 = 0, 1, 2, 3, 4, 5, 6
 KVP_I32_F32, KVP_I32_F64, KVP_I32_I16, KVP_I32_I32 = 16, 17, 18, 19
@@ -62,6 +62,14 @@ SIGNATURES = {
     "b2r_column_sum_f32_noalloc_max_scratch": (_sz, []),
     "b2r_apply_final": (ctypes.c_int, [_vp, _i32, _i64, _i32, _dbl, _vp]),
     "b2r_synth_fill": (ctypes.c_int, [_vp, _i32, _i64, _i64, _u64, _i32, _dbl, _dbl, _vp]),
+    "b2r_peer_area_create": (ctypes.c_int, [_i32, _i32, _sz, ctypes.POINTER(ctypes.c_void_p)]),
+    "b2r_peer_area_ipc_handle": (ctypes.c_int, [_vp, _vp]),
+    "b2r_peer_area_open": (ctypes.c_int, [_vp, _i32, _vp]),
+    "b2r_peer_area_link": (ctypes.c_int, [_vp, _i32, _vp]),
+    "b2r_peer_area_set_wait_limit_ms": (ctypes.c_int, [_vp, ctypes.c_uint32]),
+    "b2r_peer_allreduce_sum": (ctypes.c_int, [_vp, _vp, _i64, _vp, _i64, _dbl, _vp]),
+    "b2r_peer_area_status": (ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_int32), _i32]),
+    "b2r_peer_area_destroy": (ctypes.c_int, [_vp]),
     "b2r_probe_empty_launch": (ctypes.c_int, [_vp]),
     "b2r_probe_stream_read": (ctypes.c_int, [_vp, _sz, _vp, _vp]),
     "b2r_trim_scratch_pool": (ctypes.c_int, []),

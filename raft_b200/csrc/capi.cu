@@ -275,6 +275,7 @@ const char* b2r_status_string(int status)
     case B2R_ERR_UNSUPPORTED: return "unsupported dtype / operator combination";
     case B2R_ERR_CUDA: return "CUDA runtime error (see b2r_last_cuda_error)";
     case B2R_ERR_TOO_LARGE: return "size beyond the limit of this entry point";
+    case B2R_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
     default: return "unknown status";
   }
 }

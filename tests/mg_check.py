@@ -30,6 +30,13 @@ def main():
     linf = D.reduce_columns(shard, n, main_op="abs", reduce_op="max", init=0.0)
     sums, counts = D.reduce_rows_by_key(shard, keys, nkeys)
     norms = D.reduce_rows(shard, main_op="sq", final_op="sqrt")
+    # the same through the one-kernel all-reduce over peer memory, three times (both data sets of the area)
+    peer = D.PeerExchange(nkeys * d * 4 + nkeys * 8 + 64)
+    for _ in range(3):
+        p_mean = D.reduce_columns(shard, n, final_op="div_const", final_scalar=float(n), peer=peer)
+        p_sums, p_counts = D.reduce_rows_by_key(shard, keys, nkeys, peer=peer)
+    peer_ok = peer.status()
+    peer.close()
 
     sizes = [D.shard_rows(n, r, world) for r in range(world)]
     longest = max(b - a for a, b in sizes)
@@ -55,6 +62,10 @@ def main():
             "keyed sums": torch.allclose(sums, e_sums, rtol=1e-5, atol=1e-5),
             "key counts": torch.equal(counts, e_counts),
             "row norms (disjoint slices)": torch.equal(whole, e_norms),
+            "peer exchange: no wait ran out": peer_ok == 0,
+            "peer exchange: column mean": torch.allclose(p_mean, e_mean, rtol=1e-5, atol=1e-5),
+            "peer exchange: keyed sums": torch.allclose(p_sums, e_sums, rtol=1e-5, atol=1e-5),
+            "peer exchange: key counts": torch.equal(p_counts, e_counts),
         }
         for k, v in checks.items():
             print(("ok   " if v else "FAIL ") + k, flush=True)
