@@ -189,7 +189,10 @@ B2R_API size_t b2r_reduce_rows_by_key_workspace_bytes(
  * raft::linalg::reduce_cols_by_key - linalg/reduce_cols_by_key.cuh:39-50, 76-102, impl
  * linalg/detail/reduce_cols_by_key.cuh:89-138:
  *     out[r][keys[c]] += data[r][c]        data row-major [nrows x ncols], out [nrows x nkeys]
- * dtype: B2R_F32 or B2R_F64; key_dtype: B2R_I32, B2R_U32 or B2R_I64.
+ * dtype: B2R_F32 or B2R_F64; key_dtype: B2R_I32, B2R_U32 or B2R_I64. The reference is stateless and the
+ * caller owns every buffer (docs/source/developer_guide.md:77-81): `workspace` of
+ * b2r_reduce_cols_by_key_workspace_bytes() bytes keeps the call allocation-free (the sorted column
+ * offsets and per-split tables of the large-input algorithm; 0 for small inputs).
  */
 B2R_API int b2r_reduce_cols_by_key(void* out,
                                    const void* data,
@@ -200,7 +203,12 @@ B2R_API int b2r_reduce_cols_by_key(void* out,
                                    int64_t ncols,
                                    int64_t nkeys,
                                    int32_t reset,
+                                   void* workspace,
+                                   size_t workspace_bytes,
                                    b2r_stream_t stream);
+
+B2R_API size_t b2r_reduce_cols_by_key_workspace_bytes(
+  const void* data, int32_t dtype, int64_t nrows, int64_t ncols, int64_t nkeys);
 
 /*
  * raft::linalg::row_normalize<norm_type> - linalg/normalize.cuh:88-107, kernels
@@ -367,6 +375,22 @@ B2R_API int b2r_trim_scratch_pool(void);
  * sweeps them within one process. It must not run concurrently with other calls.
  */
 B2R_API int b2r_reload_tuning(void);
+
+/*
+ * Kernels of this library that stage tiles through shared memory wait on hardware barriers; every such
+ * wait is bounded (a second unless changed here; B2R_WAIT_LIMIT_MS sets the default of a process). A CTA
+ * whose wait runs out stops, lets its copies in flight land, fills the floating-point outputs it did not
+ * finish with NaN and sets a status word on its device; the call itself has long returned (it is
+ * asynchronous, as launch errors are in the reference: util/kernel_launch.hpp:41-42), so the outcome is
+ * read afterwards:
+ *  b2r_last_kernel_status   after the caller's own synchronisation: *status_out = B2R_ERR_TIMEOUT if a wait
+ *                           of any earlier call on the CURRENT device ran out, else B2R_OK (the reference's
+ *                           comms report SUCCESS / ERROR / ABORT the same way, core/comms.hpp:31-35);
+ *                           `clear` resets the word. Synchronising itself (a small device-to-host copy).
+ *  b2r_set_wait_limit_ms    the bound of every wait, for calls made from now on; 0 = back to the default.
+ */
+B2R_API int b2r_last_kernel_status(int32_t* status_out, int32_t clear);
+B2R_API int b2r_set_wait_limit_ms(uint32_t ms);
 
 B2R_API const char* b2r_status_string(int status);
 B2R_API int b2r_last_cuda_error(void);

@@ -8,10 +8,12 @@
 // 16-byte shared-memory loads and keep the same per-column accumulators as col_partial_kernel.
 // Output protocol (partial rows, finalize kernel) is that of col_reduce.cuh.
 //
-// Every wait on an mbarrier is bounded: after kSpinLimit failed polls a thread raises the CTA's
-// abort flag; all threads then leave their loops, the producer drains the copies it still has in
-// flight (bounded as well), marks cta_status[cta] = 1 and the CTA finishes normally. The finalize
-// kernel turns any marked CTA into NaN outputs, so a give-up is loud, not a silently wrong sum.
+// Every wait on an mbarrier is bounded by TIME (RingCtl::limit_ns of the global timer, a second by
+// default): a thread whose wait runs out raises the CTA's abort flag; all threads then leave their
+// loops, the producer drains the copies it still has in flight (bounded as well), marks
+// cta_status[cta] = 1 and the call's status word, and the CTA finishes normally. The finalize kernel
+// turns any marked CTA into NaN outputs and the host can read the status word afterwards
+// (b2r_last_kernel_status), so a give-up is loud, not a silently wrong sum.
 #pragma once
 
 #include "col_reduce.cuh"
@@ -21,8 +23,33 @@ namespace detail {
 
 constexpr int kTmaConsumers = 256;              // consumer threads (8 warps)
 constexpr int kTmaThreads   = kTmaConsumers + 32;  // + one producer warp
-constexpr unsigned kSpinLimit = 1u << 24;
 constexpr int kTmaMaxStages   = 8;
+
+// What every ring kernel is told about its waits. `status` is a device word shared by the calls of one
+// device (null: none): a CTA that gives up stores 1 there. `skip_tile` is a test hook: the producer of
+// CTA 0 does not issue the copy of that tile (-1: none), so the consumers' wait for it runs out with no
+// copy of that tile in flight - the one way to see the give-up path work without a fault.
+struct RingCtl {
+  int* status;
+  unsigned long long limit_ns;
+  int skip_tile;
+};
+constexpr unsigned long long kDefaultWaitLimitNs = 1000ull * 1000ull * 1000ull;
+B2R_HDI RingCtl default_ring_ctl()
+{
+  RingCtl c;
+  c.status    = nullptr;
+  c.limit_ns  = kDefaultWaitLimitNs;
+  c.skip_tile = -1;
+  return c;
+}
+
+B2R_DI unsigned long long ring_timer_ns()
+{
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 B2R_DI uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -50,16 +77,45 @@ B2R_DI bool mbar_try_wait(uint64_t* bar, unsigned parity)
     : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false (and raises the abort flag) when the limit is hit or another
-// thread has already aborted.
-B2R_DI bool mbar_wait_bounded(uint64_t* bar, unsigned parity, volatile int* abort_flag)
+// Bounded wait. Returns false (and raises the abort flag) when `limit_ns` has passed or another
+// thread has already aborted. The clock is only read once a first batch of polls has failed.
+B2R_DI bool mbar_wait_bounded(uint64_t* bar, unsigned parity, volatile int* abort_flag, unsigned long long limit_ns)
 {
-  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+  for (int i = 0; i < 32; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 1023u) == 1023u && *abort_flag != 0) return false;
+  const unsigned long long t0 = ring_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (ring_timer_ns() - t0 > limit_ns) break;
   }
   *abort_flag = 1;
   return false;
+}
+// The producer's last duty after a give-up: the copies it has issued must land before the CTA may exit.
+// Bounded as well (twice the limit); returns false if even that ran out.
+B2R_DI bool mbar_drain_bounded(uint64_t* bar, unsigned parity, unsigned long long limit_ns)
+{
+  const unsigned long long t0 = ring_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (ring_timer_ns() - t0 > 2 * limit_ns) return false;
+  }
+}
+// After its last copy the producer stays until the consumers have released every tile it issued, or
+// somebody has given up: it is the thread that lets copies in flight land and reports, so it leaves last.
+B2R_DI void producer_wait_released(uint64_t* s_empty, long long issued, int STAGES, volatile int* abort_flag,
+                                   unsigned long long limit_ns)
+{
+  const long long first = issued > STAGES ? issued - STAGES : 0;
+  for (long long t = first; t < issued; ++t)
+    if (!mbar_wait_bounded(&s_empty[t % STAGES], unsigned(t / STAGES) & 1u, abort_flag, limit_ns)) return;
+}
+B2R_DI void ring_report_timeout(const RingCtl& ctl)
+{
+  if (ctl.status != nullptr) atomicExch(ctl.status, 1);
 }
 B2R_DI void bulk_load(void* smem_dst, const void* gmem_src, unsigned bytes, uint64_t* bar)
 {
@@ -91,7 +147,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
                          int tile_rows,
                          int64_t rows_per_cta,
                          int STAGES,
-                         int* __restrict__ cta_status)
+                         int* __restrict__ cta_status,
+                         RingCtl ctl)
 {
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
@@ -145,7 +202,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
       for (int t = 0; t < n_tiles; ++t) {
         const int s          = t % STAGES;
         const unsigned phase = (t / STAGES) & 1u;
-        if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag)) break;
+        if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag, ctl.limit_ns)) break;
+        if (t == ctl.skip_tile && blockIdx.x == 0) continue;  // test hook: this tile is never requested
         const int64_t row0 = r_beg + int64_t(t) * tile_rows;
         const int64_t nr   = (r_end - row0) < tile_rows ? (r_end - row0) : tile_rows;
         const unsigned nb  = unsigned(size_t(nr) * row_bytes);
@@ -154,14 +212,16 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
                   &s_full[s]);
         issued = t + 1;
       }
+      producer_wait_released(s_empty, issued, STAGES, abort_flag, ctl.limit_ns);
       if (*abort_flag != 0) {
         // drain: copies already issued must land before the CTA may exit
         const int first = issued > STAGES ? issued - STAGES : 0;
         for (int t = first; t < issued; ++t) {
-          unsigned spin = 0;
-          while (!mbar_try_wait(&s_full[t % STAGES], (t / STAGES) & 1u) && ++spin < kSpinLimit) {}
+          if (t == ctl.skip_tile && blockIdx.x == 0) continue;
+          mbar_drain_bounded(&s_full[t % STAGES], (t / STAGES) & 1u, ctl.limit_ns);
         }
         if (cta_status != nullptr) cta_status[blockIdx.x] = 1;
+        ring_report_timeout(ctl);
       }
     }
   } else {
@@ -169,7 +229,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
     for (int t = 0; t < n_tiles; ++t) {
       const int s          = t % STAGES;
       const unsigned phase = (t / STAGES) & 1u;
-      if (!mbar_wait_bounded(&s_full[s], phase, abort_flag)) break;
+      if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) break;
       const int64_t row0 = r_beg + int64_t(t) * tile_rows;
       const int nr       = int((r_end - row0) < tile_rows ? (r_end - row0) : tile_rows);
       if (tx * VEC < n_cols) {

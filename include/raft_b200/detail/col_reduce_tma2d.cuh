@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
                            FinalOp final_op,
                            int64_t rows_per_cta,
                            int STAGES,
-                           int* __restrict__ cta_status)
+                           int* __restrict__ cta_status,
+                           RingCtl ctl)
 {
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
@@ -89,19 +90,22 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
       for (int t = 0; t < n_tiles; ++t) {
         const int s          = t % STAGES;
         const unsigned phase = (t / STAGES) & 1u;
-        if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag)) break;
+        if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag, ctl.limit_ns)) break;
+        if (t == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) continue;  // test hook: never requested
         mbar_expect_tx(&s_full[s], unsigned(kBoxBytes));  // the whole box, zero fill included
         tma_load_2d(tiles + size_t(s) * kBoxBytes, &tmap, int(col0), int(r_beg + int64_t(t) * kBoxRows), &s_full[s]);
         issued = t + 1;
       }
+      producer_wait_released(s_empty, issued, STAGES, abort_flag, ctl.limit_ns);
       if (*abort_flag != 0) {
         // drain: copies already issued must land before the CTA may exit
         const int first = issued > STAGES ? issued - STAGES : 0;
         for (int t = first; t < issued; ++t) {
-          unsigned spin = 0;
-          while (!mbar_try_wait(&s_full[t % STAGES], (t / STAGES) & 1u) && ++spin < kSpinLimit) {}
+          if (t == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) continue;
+          mbar_drain_bounded(&s_full[t % STAGES], (t / STAGES) & 1u, ctl.limit_ns);
         }
         if (cta_status != nullptr) cta_status[blockIdx.y] = 1;
+        ring_report_timeout(ctl);
       }
     }
   } else {
@@ -109,7 +113,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
     for (int t = 0; t < n_tiles; ++t) {
       const int s          = t % STAGES;
       const unsigned phase = (t / STAGES) & 1u;
-      if (!mbar_wait_bounded(&s_full[s], phase, abort_flag)) break;
+      if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) break;
       const int64_t row0 = r_beg + int64_t(t) * kBoxRows;
       const int nr       = int((r_end - row0) < kBoxRows ? (r_end - row0) : kBoxRows);
       if (col_ok) {

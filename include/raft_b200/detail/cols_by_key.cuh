@@ -91,6 +91,20 @@ __global__ void __launch_bounds__(256) cols_by_key_atomic_kernel(T* __restrict__
   }
 }
 
+// Scratch the call will use (what a caller passes as workspace to keep it allocation-free): the sorted
+// column offsets, the segment starts and - when the columns of a row are split over CTAs - the fp64 tables
+// of the sorted-tile algorithm; nothing for the shared-memory-atomics kernels.
+template <typename T>
+inline size_t cols_by_key_scratch_bytes(const T* data, int64_t nrows, int64_t ncols, int64_t nkeys)
+{
+  if (nrows <= 0 || ncols <= 0 || nkeys <= 0) return 0;
+  const int algo = tuning().colkey_algo;
+  if (algo != 1 && cols_by_key_sorted_supported<T>(nrows, ncols, nkeys) &&
+      (algo == 2 || cols_by_key_sorted_preferred<T>(nrows, ncols, nkeys)))
+    return plan_cols_by_key_sorted<T>(data, nrows, ncols, nkeys).total;
+  return 0;
+}
+
 template <typename T, typename KeyT>
 cudaError_t launch_cols_by_key(T* out,
                                const T* data,
@@ -99,7 +113,8 @@ cudaError_t launch_cols_by_key(T* out,
                                int64_t ncols,
                                int64_t nkeys,
                                bool reset,
-                               cudaStream_t stream)
+                               cudaStream_t stream,
+                               Workspace ws = Workspace{})
 {
   if (nrows <= 0 || nkeys <= 0) return cudaSuccess;
   cudaError_t e;
@@ -109,7 +124,7 @@ cudaError_t launch_cols_by_key(T* out,
   const int algo = tuning().colkey_algo;
   if (algo != 1 && cols_by_key_sorted_supported<T>(nrows, ncols, nkeys) &&
       (algo == 2 || cols_by_key_sorted_preferred<T>(nrows, ncols, nkeys)))
-    return launch_cols_by_key_sorted<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream);
+    return launch_cols_by_key_sorted<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream, ws);
 
   const size_t budget  = size_t(96) << 10;  // two CTAs per SM keep loads in flight across the flush
   const size_t per_row = size_t(nkeys) * sizeof(T);

@@ -376,7 +376,8 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __re
                                                                        int STAGES,
                                                                        bool reset,
                                                                        CbkStage lay,
-                                                                       size_t acc_bytes)
+                                                                       size_t acc_bytes,
+                                                                       RingCtl ctl)
 {
   extern __shared__ __align__(128) unsigned char smem_tma[];
   double* acc           = reinterpret_cast<double*>(smem_tma);  // [S][nkeys][RT]
@@ -437,9 +438,13 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __re
         for (int c = 0; c < n_ch; ++c) {
           const int s          = int(issued % STAGES);
           const unsigned phase = unsigned(issued / STAGES) & 1u;
-          if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag)) {
+          if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag, ctl.limit_ns)) {
             alive = false;
             break;
+          }
+          if (issued == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) {  // test hook: never requested
+            ++issued;
+            continue;
           }
           const int ch       = ch0 + c;
           const int64_t c0   = int64_t(ch) * CH;
@@ -456,13 +461,15 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __re
           ++issued;
         }
       }
+      if (alive) producer_wait_released(s_empty, issued, STAGES, abort_flag, ctl.limit_ns);
       if (*abort_flag != 0) {
         // drain: copies already issued must land before the CTA may exit
         const long long first = issued > STAGES ? issued - STAGES : 0;
         for (long long t = first; t < issued; ++t) {
-          unsigned spin = 0;
-          while (!mbar_try_wait(&s_full[t % STAGES], unsigned(t / STAGES) & 1u) && ++spin < kSpinLimit) {}
+          if (t == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) continue;
+          mbar_drain_bounded(&s_full[t % STAGES], unsigned(t / STAGES) & 1u, ctl.limit_ns);
         }
+        ring_report_timeout(ctl);
       }
     }
   } else {
@@ -493,7 +500,7 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __re
         if (dead) continue;
         const int s          = int(seq % STAGES);
         const unsigned phase = unsigned(seq / STAGES) & 1u;
-        if (!mbar_wait_bounded(&s_full[s], phase, abort_flag)) {
+        if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) {
           dead = true;
           continue;
         }
@@ -703,11 +710,12 @@ cudaError_t launch_cols_by_key_sorted(T* out,
                                       int64_t ncols,
                                       int64_t nkeys,
                                       bool reset,
-                                      cudaStream_t stream)
+                                      cudaStream_t stream,
+                                      Workspace ws = Workspace{})
 {
   constexpr int V16 = vec16<T>::value;
   const CbkPlan p   = plan_cols_by_key_sorted<T>(data, nrows, ncols, nkeys);
-  Scratch scratch(Workspace{}, p.total, stream);
+  Scratch scratch(ws, p.total, stream);
   if (scratch.error() != cudaSuccess) return scratch.error();
   unsigned char* base    = static_cast<unsigned char*>(scratch.get());
   unsigned short* perm16 = reinterpret_cast<unsigned short*>(base + p.off_perm);
@@ -730,7 +738,8 @@ cudaError_t launch_cols_by_key_sorted(T* out,
     const dim3 grid{unsigned(ceil_div<int64_t>(p.n_row_tiles, p.row_tiles_per_cta)), unsigned(p.y_split), 1u};
     kern<<<grid, kCbkTmaThreads, p.smem, stream>>>(out, partial, data, perm16, offs16, nrows, ncols, nk, p.RT, p.CH,
                                                    p.offs_stride, p.n_chunks, p.chunks_per_cta, p.n_row_tiles,
-                                                   p.row_tiles_per_cta, p.stages, reset, stage, p.acc_bytes);
+                                                   p.row_tiles_per_cta, p.stages, reset, stage, p.acc_bytes,
+                                                   ring_ctl(ws.status));
   } else {
   const CbkSmem<T> lay = cbk_smem<T>(p.RT, p.CH, nk);
   const dim3 grid{unsigned(p.n_row_tiles), unsigned(p.y_split), 1u};

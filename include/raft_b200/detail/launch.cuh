@@ -27,6 +27,7 @@ namespace detail {
 struct Workspace {
   void* ptr    = nullptr;
   size_t bytes = 0;
+  int* status  = nullptr;  // device word that a ring kernel whose bounded wait ran out sets to 1 (null: none)
 };
 
 // Library-owned stream-ordered memory pool, one per device, created on first use. The device's
@@ -38,8 +39,10 @@ inline cudaMemPool_t scratch_pool()
 {
   static cudaMemPool_t pools[64] = {};
   static bool tried[64]          = {};
+  static std::mutex lock;
   int dev                        = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> g(lock);  // first use on a device from several host threads at once
   if (!tried[dev]) {
     tried[dev]            = true;
     cudaMemPoolProps prop = {};
@@ -93,17 +96,17 @@ class Scratch {
 
 inline int sm_count()
 {
-  static int cached[64] = {};
-  int dev               = 0;
+  static std::atomic<int> cached[64];  // zero-initialised; a racing first use stores the same value twice
+  int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 148;
   if (dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 // Launch-shape knobs. The defaults are the measured best on B200; the environment
@@ -139,6 +142,8 @@ struct Tuning {
   int row_staged_wide_min_kb = 131072;  // B2R_ROW_STAGED_WIDE_MIN_KB the same for longer rows off the boundaries; twice that on them
   int row_staged_tile_kb   = 48;    // B2R_ROW_STAGED_KB tile size of that ring, KiB
   int row_staged_ring_kb   = 100;   // B2R_ROW_STAGED_RING_KB shared memory of one CTA's ring, KiB (100: two CTAs per SM)
+  int wait_limit_ms        = 1000;  // B2R_WAIT_LIMIT_MS bound of every mbarrier wait inside the ring kernels, milliseconds
+  int test_skip_tile       = 0;     // B2R_TEST_SKIP_TILE test hook: the producer of the first CTA never requests tile (value - 1)
 };
 
 inline int env_int(const char* name, int dflt)
@@ -187,6 +192,8 @@ inline Tuning read_tuning_from_env()
   x.row_staged_tile_kb   = env_int("B2R_ROW_STAGED_KB", x.row_staged_tile_kb);
   x.row_staged_ring_kb   = env_int("B2R_ROW_STAGED_RING_KB", x.row_staged_ring_kb);
   if (x.row_staged_ring_kb > 200) x.row_staged_ring_kb = 200;
+  x.wait_limit_ms        = env_int("B2R_WAIT_LIMIT_MS", x.wait_limit_ms);
+  x.test_skip_tile       = env_int("B2R_TEST_SKIP_TILE", x.test_skip_tile);
   return x;
 }
 
@@ -221,6 +228,22 @@ inline void reload_tuning()
   std::lock_guard<std::mutex> g(c.lock);
   c.value = read_tuning_from_env();
   c.ready.store(true, std::memory_order_release);
+}
+
+// Bound of the waits inside the ring kernels: the knob, unless the process has set one (b2r_set_wait_limit_ms).
+inline std::atomic<unsigned>& wait_limit_override_ms()
+{
+  static std::atomic<unsigned> v{0};
+  return v;
+}
+inline RingCtl ring_ctl(int* status)
+{
+  RingCtl c;
+  c.status          = status;
+  const unsigned ov = wait_limit_override_ms().load(std::memory_order_relaxed);
+  c.limit_ns        = (unsigned long long)(ov != 0 ? ov : unsigned(tuning().wait_limit_ms)) * 1000000ull;
+  c.skip_tile       = tuning().test_skip_tile - 1;
+  return c;
 }
 
 // Opt-in to more than 48 KB of dynamic shared memory, remembered per (kernel, device): the driver
@@ -513,7 +536,7 @@ cudaError_t launch_row_reduce(StoreT* out,
     if (ea != cudaSuccess) return ea;                                                                          \
     kern<<<unsigned(ctas), kRingTeams * kTmaConsumers + 32, smem, stream>>>(                                   \
       out, data, n_rows, int(row_len), init, inplace, main_op, reduce_op, final_op, G, int(tile_rows), rpc,    \
-      stages, nullptr);                                                                                        \
+      stages, ring_ctl(ws.status));                                                                            \
   } while (0)
         if (cpl == 4) {
           B2R_LAUNCH_RING(U / 4, 4);
@@ -558,7 +581,7 @@ cudaError_t launch_row_reduce(StoreT* out,
     if (ea != cudaSuccess) return ea;                                                                        \
     kern<<<unsigned(ctas), kTmaThreads, smem, stream>>>(out, data, n_main, int(row_len), init, inplace,      \
                                                        main_op, reduce_op, final_op, Gs, rot, int(tile_rows), \
-                                                       rpc, stages, nullptr);                                \
+                                                       rpc, stages, ring_ctl(ws.status));                    \
   } while (0)
         if (vec_ok) {
           B2R_LAUNCH_STAGED(V16);
@@ -849,7 +872,7 @@ cudaError_t launch_col_reduce(OutT* out,
       if (ea != cudaSuccess) return ea;
       kern<<<p.grid_x, kTmaThreads, p.smem, stream>>>(out, partial, data, n_rows, int(n_cols), init, inplace, main_op,
                                                      reduce_op, final_op, p.TX, p.tile_rows, p.rows_per_cta,
-                                                     p.stages, cta_status);
+                                                     p.stages, cta_status, ring_ctl(ws.status));
       ea = cudaGetLastError();
       if (ea != cudaSuccess) return ea;
       const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));
@@ -871,7 +894,8 @@ cudaError_t launch_col_reduce(OutT* out,
         if (ea != cudaSuccess) return ea;
         const dim3 grid2(p.grid_x, p.grid_y);
         kern<<<grid2, kTmaThreads, p.smem, stream>>>(out, partial, tmap, n_rows, n_cols, init, inplace, main_op,
-                                                    reduce_op, final_op, p.rows_per_cta, p.stages, cta_status);
+                                                    reduce_op, final_op, p.rows_per_cta, p.stages, cta_status,
+                                                    ring_ctl(ws.status));
         ea = cudaGetLastError();
         if (ea != cudaSuccess) return ea;
         const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));

@@ -249,7 +249,8 @@ cudaError_t launch_row_normalize(T* out,
                                  MainOp main_op,
                                  ReduceOp reduce_op,
                                  FinalOp final_op,
-                                 cudaStream_t stream)
+                                 cudaStream_t stream,
+                                 int* status = nullptr)
 {
   if (n_rows <= 0 || n_cols <= 0) return cudaSuccess;
   constexpr int V16 = vec16<T>::value;
@@ -290,7 +291,7 @@ cudaError_t launch_row_normalize(T* out,
     if (ea != cudaSuccess) return ea;                                                                         \
     kern<<<unsigned(sp.ctas), kTmaThreads, smem, stream>>>(out, in, sp.n_main, int(n_cols), init, eps, main_op, \
                                                           reduce_op, final_op, sp.G, sp.rot, int(sp.tile_rows), \
-                                                          sp.rows_per_cta, sp.stages);                        \
+                                                          sp.rows_per_cta, sp.stages, ring_ctl(status));      \
   } while (0)
         if (vec_ok) {
           B2R_NORMALIZE_STAGED(V16);
@@ -303,7 +304,7 @@ cudaError_t launch_row_normalize(T* out,
         // the rows behind the last 16-byte boundary: the direct kernels
         return launch_row_normalize<T, IdxT, MainOp, ReduceOp, FinalOp>(out + sp.n_main * n_cols, in + sp.n_main * n_cols,
                                                                         n_rows - sp.n_main, n_cols, init, eps, main_op,
-                                                                        reduce_op, final_op, stream);
+                                                                        reduce_op, final_op, stream, status);
       }
     }
   }

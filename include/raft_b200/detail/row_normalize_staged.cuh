@@ -41,6 +41,21 @@ B2R_DI void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" :
 B2R_DI void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // barrier among the consumer warps only (the producer warp does not take part)
 B2R_DI void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kTmaConsumers) : "memory"); }
+// the same barrier, returning whether ANY consumer passed a true predicate: a decision every consumer
+// takes alike, whatever another thread does to the underlying flag in the meantime
+B2R_DI bool consumer_sync_any(bool pred)
+{
+  unsigned r;
+  asm volatile(
+    "{\n\t.reg .pred p, q;\n\t"
+    "setp.ne.u32 p, %1, 0;\n\t"
+    "bar.red.or.pred q, 1, %2, p;\n\t"
+    "selp.u32 %0, 1, 0, q;\n\t}"
+    : "=r"(r)
+    : "r"(unsigned(pred)), "n"(kTmaConsumers)
+    : "memory");
+  return r != 0;
+}
 
 template <typename T, typename IdxT, typename MainOp, typename ReduceOp, typename FinalOp, int VEC>
 __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T* out,
@@ -56,7 +71,8 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T*
                                                                              int rot,
                                                                              int tile_rows,
                                                                              int64_t rows_per_cta,
-                                                                             int STAGES)
+                                                                             int STAGES,
+                                                                             RingCtl ctl)
 {
   using State = typename state_for<T, ReduceOp>::type;
   using Vec   = VecOf<T, VEC>;
@@ -98,6 +114,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T*
       // the host makes n_rows, tile_rows and rows_per_cta multiples of the rows between two 16-byte
       // boundaries, so every copy starts on a boundary and has a legal size
       auto load = [&](int t) {
+        if (t == ctl.skip_tile && blockIdx.x == 0) return;  // test hook: this tile is never requested
         const int s        = t % STAGES;
         const int64_t row0 = r_beg + int64_t(t) * tile_rows;
         const int64_t nr   = (r_end - row0) < tile_rows ? (r_end - row0) : tile_rows;
@@ -113,7 +130,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T*
       for (; t < n_tiles; ++t) {
         const int s          = t % STAGES;
         const unsigned phase = (t / STAGES) & 1u;
-        if (!mbar_wait_bounded(&s_done[s], phase, abort_flag)) break;
+        if (!mbar_wait_bounded(&s_done[s], phase, abort_flag, ctl.limit_ns)) break;
         if (skip_flag[s] == 0) {
           const int64_t row0 = r_beg + int64_t(t) * tile_rows;
           const int64_t nr   = (r_end - row0) < tile_rows ? (r_end - row0) : tile_rows;
@@ -131,9 +148,10 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T*
       if (t < n_tiles) {
         // gave up: the loads already issued must land before the CTA may exit
         for (int u = t; u < loaded; ++u) {
-          unsigned spin = 0;
-          while (!mbar_try_wait(&s_full[u % STAGES], (u / STAGES) & 1u) && ++spin < kSpinLimit) {}
+          if (u == ctl.skip_tile && blockIdx.x == 0) continue;
+          mbar_drain_bounded(&s_full[u % STAGES], (u / STAGES) & 1u, ctl.limit_ns);
         }
+        ring_report_timeout(ctl);
       }
       bulk_store_wait_all();
     }
@@ -155,9 +173,10 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T*
   for (; t < n_tiles; ++t) {
     const int s          = t % STAGES;
     const unsigned phase = (t / STAGES) & 1u;
-    mbar_wait_bounded(&s_full[s], phase, abort_flag);
-    consumer_sync();  // a wait that ran out has raised the flag before this barrier: everybody leaves together
-    if (*abort_flag != 0) break;
+    // a wait that ran out (here, or in the producer) has raised the flag; each consumer reads it BEFORE the
+    // barrier and the barrier ORs what they saw, so all of them stay or all of them leave
+    mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns);
+    if (consumer_sync_any(*abort_flag != 0)) break;
     const int64_t tile_row0 = r_beg + int64_t(t) * tile_rows;
     const int nr            = int((r_end - tile_row0) < tile_rows ? (r_end - tile_row0) : tile_rows);
     Vec* tile               = reinterpret_cast<Vec*>(smem_tma + s * stage_stride);

@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
                                                                         int tile_rows,
                                                                         int64_t rows_per_cta,
                                                                         int STAGES,
-                                                                        int* __restrict__ status)
+                                                                        RingCtl ctl)
 {
   using State          = typename state_for<OutT, ReduceOp>::type;
   using Vec            = VecOf<InT, VEC>;
@@ -91,7 +91,8 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
       for (int t = 0; t < n_tiles; ++t) {
         const int s          = t % STAGES;
         const unsigned phase = (t / STAGES) & 1u;
-        if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag)) break;
+        if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag, ctl.limit_ns)) break;
+        if (t == ctl.skip_tile && blockIdx.x == 0) continue;  // test hook: this tile is never requested
         const int64_t row0 = r_beg + int64_t(t) * tile_rows;
         const int64_t nr   = (r_end - row0) < tile_rows ? (r_end - row0) : tile_rows;
         const unsigned nb  = unsigned(size_t(nr) * row_bytes);
@@ -100,13 +101,14 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
                   nb, &s_full[s]);
         issued = t + 1;
       }
+      producer_wait_released(s_empty, issued, STAGES, abort_flag, ctl.limit_ns);
       if (*abort_flag != 0) {
         const int first = issued > STAGES ? issued - STAGES : 0;
         for (int t = first; t < issued; ++t) {
-          unsigned spin = 0;
-          while (!mbar_try_wait(&s_full[t % STAGES], (t / STAGES) & 1u) && ++spin < kSpinLimit) {}
+          if (t == ctl.skip_tile && blockIdx.x == 0) continue;
+          mbar_drain_bounded(&s_full[t % STAGES], (t / STAGES) & 1u, ctl.limit_ns);
         }
-        if (status != nullptr) atomicExch(status, 1);
+        ring_report_timeout(ctl);
       }
     }
     return;
@@ -135,7 +137,7 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
   for (; t < n_tiles; t += TEAMS) {
     const int s          = t % STAGES;
     const unsigned phase = (t / STAGES) & 1u;
-    if (!mbar_wait_bounded(&s_full[s], phase, abort_flag)) break;
+    if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) break;
     const int64_t tile_row0 = r_beg + int64_t(t) * tile_rows;
     const int nr            = int((r_end - tile_row0) < tile_rows ? (r_end - tile_row0) : tile_rows);
     const unsigned char* tile = smem_tma + s * stage_stride;

@@ -54,7 +54,10 @@ SIGNATURES = {
     "b2r_reduce_rows_by_key": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i32,
                                               _vp, _sz, _vp]),
     "b2r_reduce_rows_by_key_workspace_bytes": (_sz, [_vp, _i64, _i32, _i64, _i64, _i64]),
-    "b2r_reduce_cols_by_key": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i32, _vp]),
+    "b2r_reduce_cols_by_key": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "b2r_reduce_cols_by_key_workspace_bytes": (_sz, [_vp, _i32, _i64, _i64, _i64]),
+    "b2r_last_kernel_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int32), _i32]),
+    "b2r_set_wait_limit_ms": (ctypes.c_int, [ctypes.c_uint32]),
     "b2r_row_normalize": (ctypes.c_int, [_vp, _vp, _i32, _i64, _i64, _i32, _dbl, _vp]),
     "b2r_matrix_argmin": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _i64, _vp]),
     "b2r_matrix_argmax": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _i64, _vp]),

@@ -6,10 +6,36 @@
 #include <raft_b200/detail/rows_by_key.cuh>
 #include <raft_b200/detail/synth.cuh>
 
+#include <mutex>
+
 namespace raft_b200 {
 namespace capi {
 
 static thread_local int g_last_cuda_error = 0;
+
+// One status word per device (a __device__ variable exists once on every device that loads the library).
+// In host code its name is only a handle: the address the kernels get comes from cudaGetSymbolAddress.
+static __device__ int g_kernel_status;
+static std::mutex g_status_mutex;
+static int* g_status_ptr[64]    = {};
+static bool g_status_tried[64]  = {};
+
+int* kernel_status_word()
+{
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_status_tried[dev]) {
+    g_status_tried[dev] = true;
+    void* p             = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kernel_status) == cudaSuccess) {
+      g_status_ptr[dev] = static_cast<int*>(p);
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  return g_status_ptr[dev];
+}
 
 int set_cuda_error(cudaError_t e)
 {
@@ -61,11 +87,11 @@ static int rows_by_key_typed(void* sums, int64_t* counts, const void* A, int64_t
 
 template <typename T, typename KeyT>
 static int cols_by_key_typed(void* out, const void* data, const void* keys, int64_t nrows, int64_t ncols,
-                             int64_t nkeys, bool reset, cudaStream_t s)
+                             int64_t nkeys, bool reset, detail::Workspace ws, cudaStream_t s)
 {
   return set_cuda_error(detail::launch_cols_by_key<T, KeyT>(
     static_cast<T*>(out), static_cast<const T*>(data), static_cast<const KeyT*>(keys), nrows, ncols, nkeys,
-    reset, s));
+    reset, s, ws));
 }
 
 }  // namespace capi
@@ -82,9 +108,7 @@ int b2r_reduce(const b2r_reduce_desc* desc, void* out, const void* in, void* wor
   const int chk = check_desc(desc, out, in);
   if (chk != B2R_OK) return chk;
   const b2r_reduce_desc& d = *desc;
-  detail::Workspace ws;
-  ws.ptr           = workspace;
-  ws.bytes         = workspace != nullptr ? workspace_bytes : 0;
+  const detail::Workspace ws = make_workspace(workspace, workspace_bytes);
   cudaStream_t s   = to_stream(stream);
   if (is_kvp(d.out_dtype)) return reduce_kvp_any(d, out, in, ws, s);
   if (d.main_op == B2R_MAIN_TO_KVP || d.reduce_op == B2R_REDUCE_ARGMIN || d.reduce_op == B2R_REDUCE_ARGMAX)
@@ -152,9 +176,7 @@ int b2r_reduce_rows_by_key(void* sums, int64_t* counts, const void* A, int64_t l
   if (nrows < 0 || ncols < 0 || nkeys < 0 || lda < ncols) return B2R_ERR_BAD_ARG;
   if (ncols > 0 && nkeys > 0 && sums == nullptr) return B2R_ERR_BAD_ARG;
   if (nrows > 0 && ncols > 0 && (A == nullptr || keys == nullptr)) return B2R_ERR_BAD_ARG;
-  detail::Workspace ws;
-  ws.ptr         = workspace;
-  ws.bytes       = workspace != nullptr ? workspace_bytes : 0;
+  const detail::Workspace ws = make_workspace(workspace, workspace_bytes);
   cudaStream_t s = to_stream(stream);
   const bool rs  = reset != 0;
 #define B2R_RBK(DT, KT) \
@@ -183,14 +205,16 @@ size_t b2r_reduce_rows_by_key_workspace_bytes(const void* A, int64_t lda, int32_
 }
 
 int b2r_reduce_cols_by_key(void* out, const void* data, const void* keys, int32_t dtype, int32_t key_dtype,
-                           int64_t nrows, int64_t ncols, int64_t nkeys, int32_t reset, b2r_stream_t stream)
+                           int64_t nrows, int64_t ncols, int64_t nkeys, int32_t reset, void* workspace,
+                           size_t workspace_bytes, b2r_stream_t stream)
 {
   if (nrows < 0 || ncols < 0 || nkeys < 0) return B2R_ERR_BAD_ARG;
   if (nrows > 0 && nkeys > 0 && out == nullptr) return B2R_ERR_BAD_ARG;
   if (nrows > 0 && ncols > 0 && (data == nullptr || keys == nullptr)) return B2R_ERR_BAD_ARG;
+  const detail::Workspace ws = make_workspace(workspace, workspace_bytes);
   cudaStream_t s = to_stream(stream);
   const bool rs  = reset != 0;
-#define B2R_CBK(DT, KT) return cols_by_key_typed<DT, KT>(out, data, keys, nrows, ncols, nkeys, rs, s)
+#define B2R_CBK(DT, KT) return cols_by_key_typed<DT, KT>(out, data, keys, nrows, ncols, nkeys, rs, ws, s)
   if (dtype == B2R_F32) {
     if (key_dtype == B2R_I32) B2R_CBK(float, int);
     if (key_dtype == B2R_U32) B2R_CBK(float, unsigned);
@@ -202,6 +226,34 @@ int b2r_reduce_cols_by_key(void* out, const void* data, const void* keys, int32_
   }
 #undef B2R_CBK
   return B2R_ERR_UNSUPPORTED;
+}
+
+size_t b2r_reduce_cols_by_key_workspace_bytes(const void* data, int32_t dtype, int64_t nrows, int64_t ncols,
+                                              int64_t nkeys)
+{
+  if (nrows <= 0 || ncols <= 0 || nkeys <= 0) return 0;
+  if (dtype == B2R_F32) return detail::cols_by_key_scratch_bytes<float>(static_cast<const float*>(data), nrows, ncols, nkeys);
+  if (dtype == B2R_F64) return detail::cols_by_key_scratch_bytes<double>(static_cast<const double*>(data), nrows, ncols, nkeys);
+  return 0;
+}
+
+int b2r_last_kernel_status(int32_t* status_out, int32_t clear)
+{
+  if (status_out == nullptr) return B2R_ERR_BAD_ARG;
+  int* word = kernel_status_word();
+  if (word == nullptr) return set_cuda_error(cudaErrorInvalidSymbol);
+  int v         = 0;
+  cudaError_t e = cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && clear != 0 && v != 0) e = cudaMemset(word, 0, sizeof(int));
+  if (e != cudaSuccess) return set_cuda_error(e);
+  *status_out = v != 0 ? B2R_ERR_TIMEOUT : B2R_OK;
+  return B2R_OK;
+}
+
+int b2r_set_wait_limit_ms(uint32_t ms)
+{
+  detail::wait_limit_override_ms().store(ms, std::memory_order_relaxed);  // 0: back to the knob / default
+  return B2R_OK;
 }
 
 int b2r_apply_final(void* v, int32_t dtype, int64_t n, int32_t final_op, double final_scalar, b2r_stream_t stream)

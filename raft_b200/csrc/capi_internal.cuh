@@ -11,6 +11,20 @@ namespace capi {
 
 int set_cuda_error(cudaError_t e);  // records e for b2r_last_cuda_error, returns B2R_ERR_CUDA / B2R_OK
 
+// Device address of the library's kernel-status word on the CURRENT device (looked up once per device), or
+// null if the lookup failed: ring kernels whose bounded wait ran out set it, b2r_last_kernel_status reads it.
+int* kernel_status_word();
+
+// A caller's workspace plus the status word, as the launchers take them.
+inline detail::Workspace make_workspace(void* workspace, size_t workspace_bytes)
+{
+  detail::Workspace ws;
+  ws.ptr    = workspace;
+  ws.bytes  = workspace != nullptr ? workspace_bytes : 0;
+  ws.status = kernel_status_word();
+  return ws;
+}
+
 inline cudaStream_t to_stream(b2r_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 // Geometry of a reduce call once layout and apply are folded together

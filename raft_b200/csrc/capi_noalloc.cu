@@ -70,8 +70,9 @@ extern "C" int b2r_column_sum_f32_noalloc(float* out, const float* in, int64_t n
   cudaError_t e = noalloc_scratch(&scratch);
   if (e != cudaSuccess) return set_cuda_error(e);
   detail::Workspace ws;
-  ws.ptr   = scratch;
-  ws.bytes = kNoAllocScratchBytes;
+  ws.ptr    = scratch;
+  ws.bytes  = kNoAllocScratchBytes;
+  ws.status = kernel_status_word();  // an address lookup on the first call per device, no allocation
   op::RuntimeFinal<float> fin{final_op, float(final_scalar)};
   e = detail::launch_col_reduce<float, float, int64_t>(out, in, n_rows, n_cols, n_cols, 0.0f, false, op::Identity{},
                                                        op::Add{}, fin, to_stream(stream), ws, kNoAllocScratchBytes);

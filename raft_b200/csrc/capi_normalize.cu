@@ -12,20 +12,21 @@ static int row_normalize(void* out_v, const void* in_v, int64_t n_rows, int64_t 
 {
   T* out      = static_cast<T*>(out_v);
   const T* in = static_cast<const T*>(in_v);
+  int* status = kernel_status_word();
   cudaError_t e;
   // the functor triples of linalg/normalize.cuh:94-103
   switch (norm_type) {
     case B2R_NORM_L1:
       e = detail::launch_row_normalize<T, int64_t>(out, in, n_rows, n_cols, T(0), T(eps), op::Abs{}, op::Add{},
-                                                   op::Identity{}, s);
+                                                   op::Identity{}, s, status);
       break;
     case B2R_NORM_L2:
       e = detail::launch_row_normalize<T, int64_t>(out, in, n_rows, n_cols, T(0), T(eps), op::Square{}, op::Add{},
-                                                   op::Sqrt{}, s);
+                                                   op::Sqrt{}, s, status);
       break;
     case B2R_NORM_LINF:
       e = detail::launch_row_normalize<T, int64_t>(out, in, n_rows, n_cols, T(0), T(eps), op::Abs{}, op::Max{},
-                                                   op::Identity{}, s);
+                                                   op::Identity{}, s, status);
       break;
     default: return B2R_ERR_UNSUPPORTED;  // the reference fails for any other norm type (normalize.cuh:104)
   }

@@ -275,9 +275,10 @@ def reduce_rows_by_key_workspace_bytes(d_A, n_unique_keys, lda=None):
                                                                nrows, ncols, n_unique_keys)
 
 
-def reduce_cols_by_key(data, keys, out=None, nkeys=0, reset_sums=True):
+def reduce_cols_by_key(data, keys, out=None, nkeys=0, reset_sums=True, workspace=None):
     """out[r, keys[c]] += data[r, c] (linalg/reduce_cols_by_key.cuh:76-102). nkeys = 0 infers
-    the number of keys from out.shape[1], as the reference does."""
+    the number of keys from out.shape[1], as the reference does. `workspace` (uint8, see
+    reduce_cols_by_key_workspace_bytes) keeps the call allocation-free."""
     _require_cuda(data, "data")
     _require_cuda(keys, "keys")
     if data.dim() != 2 or not data.is_contiguous():
@@ -299,12 +300,37 @@ def reduce_cols_by_key(data, keys, out=None, nkeys=0, reset_sums=True):
     key_dt = _KEY_DTYPES.get(keys.dtype)
     if key_dt is None or data.dtype not in (torch.float32, torch.float64) or out.dtype != data.dtype:
         raise L.B2RError(L.ERR_UNSUPPORTED, "reduce_cols_by_key")
+    ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None \
+        else (None, 0)
     with _on(data.device):
         st = L.load().b2r_reduce_cols_by_key(out.data_ptr(), data.data_ptr(), keys.data_ptr(), _DTYPES[data.dtype],
-                                             key_dt, nrows, ncols, nkeys, 1 if reset_sums else 0,
+                                             key_dt, nrows, ncols, nkeys, 1 if reset_sums else 0, ws_ptr, ws_bytes,
                                              _stream_ptr(data.device))
     L.check(st, "b2r_reduce_cols_by_key")
     return out
+
+
+def reduce_cols_by_key_workspace_bytes(data, nkeys):
+    nrows, ncols = data.shape
+    with _on(data.device):
+        return L.load().b2r_reduce_cols_by_key_workspace_bytes(data.data_ptr(), _DTYPES[data.dtype], nrows, ncols,
+                                                               nkeys)
+
+
+def last_kernel_status(device, clear=True):
+    """Synchronises `device` and returns L.OK, or L.ERR_TIMEOUT if a bounded wait inside a kernel of any
+    earlier call on that device ran out (that call's unfinished floating-point outputs are NaN)."""
+    import ctypes
+    torch.cuda.synchronize(device)
+    out = ctypes.c_int32(0)
+    with _on(device):
+        L.check(L.load().b2r_last_kernel_status(ctypes.byref(out), 1 if clear else 0), "b2r_last_kernel_status")
+    return out.value
+
+
+def set_wait_limit_ms(ms):
+    """Bound of every wait inside the kernels that stage tiles through shared memory; 0 = the default."""
+    L.check(L.load().b2r_set_wait_limit_ms(int(ms)), "b2r_set_wait_limit_ms")
 
 
 def _matrix_arg(fn_name, data, out, index_dtype):
