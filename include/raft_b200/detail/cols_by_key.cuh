@@ -2,8 +2,9 @@
 //
 // Counterpart of the reference's cached / direct kernels
 // (linalg/detail/reduce_cols_by_key.cuh:23-68, dispatch :89-138). Two algorithms:
-//  * sorted column tiles (cols_by_key_sorted.cuh) for large inputs with up to a few hundred keys:
-//    no floating-point atomics, TMA-staged tiles;
+//  * sorted column tiles for large inputs with up to a few hundred keys: no floating-point atomics,
+//    tiles staged by bulk copies - with a warp walking the sorted columns of its keys (cols_by_key_walk.cuh) for matrices of at least
+//    256 rows and up to 64 keys, with a lane per (row, key) segment (cols_by_key_sorted.cuh) otherwise;
 //  * the kernels of this file otherwise: a CTA owns a tile of RT rows and a contiguous range of
 //    columns, accumulates into a privatised [RT x nkeys] table in shared memory (shared-memory
 //    atomics; lanes of a warp read 128 contiguous bytes of one row per step) and flushes the
@@ -15,6 +16,7 @@
 #include "common.cuh"
 #include "launch.cuh"
 #include "cols_by_key_sorted.cuh"
+#include "cols_by_key_walk.cuh"
 
 namespace raft_b200 {
 namespace detail {
@@ -91,6 +93,23 @@ __global__ void __launch_bounds__(256) cols_by_key_atomic_kernel(T* __restrict__
   }
 }
 
+// Which sorted-tile form a call takes: 0 none (the kernels of this file), 1 a lane per segment, 2 a warp walking its keys.
+template <typename T>
+inline int cols_by_key_sorted_form(const T* data, int64_t nrows, int64_t ncols, int64_t nkeys, Cbk32Plan* p32)
+{
+  const int algo = tuning().colkey_algo;  // 0: by size, 1: shared-memory atomics, 2: a lane per segment, 3: a warp walking its keys
+  if (algo == 1 || !cols_by_key_sorted_supported<T>(nrows, ncols, nkeys)) return 0;
+  const bool preferred = cols_by_key_sorted_preferred<T>(nrows, ncols, nkeys);
+  if (algo == 3 || (algo == 0 && preferred && nrows >= 256 && nkeys <= tuning().colkey_walk_max_keys)) {
+    const Cbk32Plan p = plan_cols_by_key_rows32<T>(data, nrows, ncols, nkeys, tuning().colkey32_ch, tuning().colkey32_rt);
+    if (p.ok) {
+      if (p32 != nullptr) *p32 = p;
+      return 2;
+    }
+  }
+  return (algo == 2 || algo == 3 || preferred) ? 1 : 0;
+}
+
 // Scratch the call will use (what a caller passes as workspace to keep it allocation-free): the sorted
 // column offsets, the segment starts and - when the columns of a row are split over CTAs - the fp64 tables
 // of the sorted-tile algorithm; nothing for the shared-memory-atomics kernels.
@@ -98,10 +117,10 @@ template <typename T>
 inline size_t cols_by_key_scratch_bytes(const T* data, int64_t nrows, int64_t ncols, int64_t nkeys)
 {
   if (nrows <= 0 || ncols <= 0 || nkeys <= 0) return 0;
-  const int algo = tuning().colkey_algo;
-  if (algo != 1 && cols_by_key_sorted_supported<T>(nrows, ncols, nkeys) &&
-      (algo == 2 || cols_by_key_sorted_preferred<T>(nrows, ncols, nkeys)))
-    return plan_cols_by_key_sorted<T>(data, nrows, ncols, nkeys).total;
+  Cbk32Plan p32;
+  const int form = cols_by_key_sorted_form<T>(data, nrows, ncols, nkeys, &p32);
+  if (form == 2) return p32.total;
+  if (form == 1) return plan_cols_by_key_sorted<T>(data, nrows, ncols, nkeys).total;
   return 0;
 }
 
@@ -121,10 +140,12 @@ cudaError_t launch_cols_by_key(T* out,
   const size_t out_bytes = size_t(nrows) * nkeys * sizeof(T);
   if (ncols <= 0) return reset ? cudaMemsetAsync(out, 0, out_bytes, stream) : cudaSuccess;
   // sorted column tiles where they win (large inputs, a few hundred keys at most)
-  const int algo = tuning().colkey_algo;
-  if (algo != 1 && cols_by_key_sorted_supported<T>(nrows, ncols, nkeys) &&
-      (algo == 2 || cols_by_key_sorted_preferred<T>(nrows, ncols, nkeys)))
-    return launch_cols_by_key_sorted<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream, ws);
+  {
+    Cbk32Plan p32;
+    const int form = cols_by_key_sorted_form<T>(data, nrows, ncols, nkeys, &p32);
+    if (form == 2) return launch_cols_by_key_rows32<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream, p32, ws);
+    if (form == 1) return launch_cols_by_key_sorted<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream, ws);
+  }
 
   const size_t budget  = size_t(96) << 10;  // two CTAs per SM keep loads in flight across the flush
   const size_t per_row = size_t(nkeys) * sizeof(T);

@@ -429,38 +429,47 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __re
   volatile int* abort_flag = &s_abort;
 
   if (producer) {
-    if (tid == kCbkConsumers) {  // one elected thread issues every copy
-      long long issued = 0;
-      bool alive       = true;
-      for (int64_t rti = rt0; rti < rt1 && alive; ++rti) {
-        const int64_t r0 = rti * RT;
-        const int rt     = int(nrows - r0 < RT ? nrows - r0 : RT);
-        for (int c = 0; c < n_ch; ++c) {
-          const int s          = int(issued % STAGES);
-          const unsigned phase = unsigned(issued / STAGES) & 1u;
-          if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag, ctl.limit_ns)) {
-            alive = false;
-            break;
-          }
-          if (issued == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) {  // test hook: never requested
-            ++issued;
-            continue;
-          }
-          const int ch       = ch0 + c;
-          const int64_t c0   = int64_t(ch) * CH;
-          const int cw       = int(ncols - c0 < CH ? ncols - c0 : CH);
-          unsigned char* st  = stages + size_t(s) * lay.bytes;
-          const unsigned rb  = unsigned(cw) * unsigned(sizeof(T));           // a multiple of 16
-          const unsigned pb  = unsigned(CH) * unsigned(sizeof(unsigned short));
-          const unsigned ob  = unsigned(offs_stride) * unsigned(sizeof(unsigned short));
-          mbar_expect_tx(&s_full[s], rb * unsigned(rt) + pb + ob);
-          for (int r = 0; r < rt; ++r)
-            bulk_load(st + lay.off_tile + size_t(r) * stride * sizeof(T), data + (r0 + r) * ncols + c0, rb, &s_full[s]);
-          bulk_load(st + lay.off_perm, perm16 + size_t(ch) * CH, pb, &s_full[s]);
-          bulk_load(st + lay.off_offs, offs16 + size_t(ch) * offs_stride, ob, &s_full[s]);
-          ++issued;
+    // The producer WARP: lane 0 waits for the stage and announces the bytes, then every copy of the stage is
+    // issued by a lane of its own - RT row pieces, the sorted offsets, the segment starts - so a stage costs
+    // the issue time of one copy instead of RT + 2 (one issuing thread was what bounded the kernel with few
+    // keys: 5.1 TB/s with the consumers switched off).
+    const int plane  = tid - kCbkConsumers;
+    long long issued = 0;
+    bool alive       = true;
+    for (int64_t rti = rt0; rti < rt1 && alive; ++rti) {
+      const int64_t r0 = rti * RT;
+      const int rt     = int(nrows - r0 < RT ? nrows - r0 : RT);
+      for (int c = 0; c < n_ch; ++c) {
+        const int s          = int(issued % STAGES);
+        const unsigned phase = unsigned(issued / STAGES) & 1u;
+        int ok               = 1;
+        if (plane == 0) ok = mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag, ctl.limit_ns) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          alive = false;
+          break;
         }
+        if (issued == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) {  // test hook: never requested
+          ++issued;
+          continue;
+        }
+        const int ch       = ch0 + c;
+        const int64_t c0   = int64_t(ch) * CH;
+        const int cw       = int(ncols - c0 < CH ? ncols - c0 : CH);
+        unsigned char* st  = stages + size_t(s) * lay.bytes;
+        const unsigned rb  = unsigned(cw) * unsigned(sizeof(T));           // a multiple of 16
+        const unsigned pb  = unsigned(CH) * unsigned(sizeof(unsigned short));
+        const unsigned ob  = unsigned(offs_stride) * unsigned(sizeof(unsigned short));
+        if (plane == 0) mbar_expect_tx(&s_full[s], rb * unsigned(rt) + pb + ob);
+        __syncwarp();  // the bytes are announced before any copy can complete
+        for (int r = plane; r < rt; r += 32)
+          bulk_load(st + lay.off_tile + size_t(r) * stride * sizeof(T), data + (r0 + r) * ncols + c0, rb, &s_full[s]);
+        if (plane == (rt & 31)) bulk_load(st + lay.off_perm, perm16 + size_t(ch) * CH, pb, &s_full[s]);
+        if (plane == ((rt + 1) & 31)) bulk_load(st + lay.off_offs, offs16 + size_t(ch) * offs_stride, ob, &s_full[s]);
+        ++issued;
       }
+    }
+    if (plane == 0) {
       if (alive) producer_wait_released(s_empty, issued, STAGES, abort_flag, ctl.limit_ns);
       if (*abort_flag != 0) {
         // drain: copies already issued must land before the CTA may exit

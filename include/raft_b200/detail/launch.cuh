@@ -120,7 +120,10 @@ struct Tuning {
   int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
   int key_algo             = 0;     // B2R_KEY_ALGO   0: by size, 1: shared-memory table, 2: sort then stream, 3: one-launch kernel (<= 32768 rows)
-  int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted column tiles
+  int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted tiles, a lane per segment, 3: sorted tiles, a warp walking its keys
+  int colkey32_ch          = 0;     // B2R_COLKEY32_CH columns per chunk of the walk form of the keyed column sums (0: the longest that fits)
+  int colkey32_rt          = 16;    // B2R_COLKEY32_RT rows per tile of that form: 8, 16 or 32
+  int colkey_walk_max_keys = 64;    // B2R_COLKEY_WALK_MAX most keys for which that form is chosen by itself
   int colkey_tma           = 1;     // B2R_COLKEY_TMA 1: TMA-staged ring for the sorted column tiles, 2: off
   int col_tma              = 1;     // B2R_COL_TMA    1: TMA-staged tiles for narrow contiguous column reductions, 2: off
   int col_tma_tile_kb      = 32;    // B2R_COL_TMA_KB tile size of the TMA ring, KiB
@@ -166,6 +169,9 @@ inline Tuning read_tuning_from_env()
   x.key_window_rows      = env_int("B2R_KEY_WINDOW", x.key_window_rows);
   x.key_algo             = env_int("B2R_KEY_ALGO", x.key_algo);
   x.colkey_algo          = env_int("B2R_COLKEY_ALGO", x.colkey_algo);
+  x.colkey32_ch          = env_int("B2R_COLKEY32_CH", x.colkey32_ch);
+  x.colkey32_rt          = env_int("B2R_COLKEY32_RT", x.colkey32_rt);
+  x.colkey_walk_max_keys = env_int("B2R_COLKEY_WALK_MAX", x.colkey_walk_max_keys);
   x.colkey_tma           = env_int("B2R_COLKEY_TMA", x.colkey_tma);
   x.col_tma              = env_int("B2R_COL_TMA", x.col_tma);
   x.col_tma_tile_kb      = env_int("B2R_COL_TMA_KB", x.col_tma_tile_kb);

@@ -4,7 +4,8 @@
 # the small C ABI of oracle/ref_*.cu. Test infrastructure: used to validate the CPU oracle and
 # as the "reference" column of the benchmark.
 #
-#   oracle/build_ref.sh [path of the reference checkout; default: REF below]
+#   oracle/build_ref.sh [path of the reference checkout; default: $RAFT_REFERENCE_DIR, else a directory
+#                        named `reference` beside this repository]
 #
 # The reference's cmake build cannot configure offline (it fetches rapids-cmake, rmm,
 # rapids_logger, gtest), but this path is header-only; it needs
@@ -13,7 +14,7 @@
 # Exits 0 without building when the reference checkout or that CCCL is absent.
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${RAFT_REFERENCE_DIR:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 CCCL="$(python - <<'PY'
 import importlib.util, os

@@ -191,6 +191,31 @@ def test_cols_by_key_sorted_tiles(cuda, oracle, knobs, rows, cols, nkeys, dt, to
         assert torch.equal(again, linalg.reduce_cols_by_key(data, keys, nkeys=nkeys))
 
 
+# the walk form of the sorted tiles (a warp walks the sorted columns of its keys; up to 256 keys), forced, on every
+# tile shape it has (8 / 16 / 32 rows), with ragged last chunks and row tiles, columns split over CTAs or not,
+# fewer keys than warps (slices), a caller's workspace, and a key that owns no column
+@pytest.mark.parametrize("rows,cols,nkeys", [(1, 1236, 7), (9, 10000, 42), (63, 101012, 127), (1024, 1236, 7),
+                                             (1024, 9996, 256), (4001, 4100, 3), (300, 50004, 1), (20000, 256, 5),
+                                             (7, 8, 4), (2000, 30000, 16), (2000, 30000, 64), (33, 70000, 200)])
+@pytest.mark.parametrize("dt,tol", [(np.float32, 1e-5), (np.float64, 1e-9)])
+@pytest.mark.parametrize("rt", [8, 16, 32])
+def test_cols_by_key_walk_form(cuda, oracle, knobs, rows, cols, nkeys, dt, tol, rt):
+    knobs(B2R_COLKEY_ALGO="3", B2R_COLKEY32_RT=str(rt))
+    data, hd = device_synth((rows, cols), dt, 1234, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((cols,), np.int32, 55, "int", 0, max(1, nkeys - 1), cuda)  # the last key stays empty
+    ws = torch.empty(max(1, linalg.reduce_cols_by_key_workspace_bytes(data, nkeys)), dtype=torch.uint8, device=cuda)
+    out = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys, workspace=ws)
+    exp = oracle.cols_by_key(hd, hk, nkeys)
+    oracle.assert_approx(exp, out.cpu().numpy(), tol, "reset")
+    linalg.reduce_cols_by_key(data, keys, out=out, reset_sums=False)
+    oracle.assert_approx(2 * exp, out.cpu().numpy(), 2 * tol, "accumulate")
+    # no floating-point atomics: a repeat gives the same bits (fp64 partial sums of fp32 data)
+    if dt == np.float32:
+        again = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys)
+        assert torch.equal(again, linalg.reduce_cols_by_key(data, keys, nkeys=nkeys))
+    assert linalg.last_kernel_status(cuda) == 0
+
+
 def test_cols_by_key_single_kernel_path(cuda, oracle, knobs):
     knobs(B2R_COLKEY_ALGO="1")
     data, hd = device_synth((2000, 3000), np.float32, 3, "uniform", -1, 1, cuda)

@@ -46,6 +46,19 @@ def _worker(rank, world, port, q):
         part = torch.from_numpy(o.reduce(full[r0:r1], apply=1))
         D.combine_partials(part, "add")
         ok = np.allclose(part.numpy(), o.reduce(full, apply=1), rtol=1e-12)
+        # a sum's start value enters the total ONCE (rank 0 keeps it, the others start from zero); the
+        # start value of a max is idempotent and stays on every rank
+        init = 3.5
+        part = torch.from_numpy(o.reduce(full[r0:r1], apply=1, init=D._init_for_rank(init, "add", None)))
+        D.combine_partials(part, "add")
+        ok = ok and np.allclose(part.numpy(), o.reduce(full, apply=1, init=init), rtol=1e-12)
+        ok = ok and D._init_for_rank(init, "max", None) == init
+        # several partials at once: tensors of one type as a group, other types by themselves
+        a, b = torch.full((5,), float(rank + 1)), torch.full((3,), rank + 1, dtype=torch.int64)
+        c = torch.full((2,), float(10 * (rank + 1)))
+        D.combine_partials_grouped([a, None, b, c], "add")
+        tot = sum(range(1, world + 1))
+        ok = ok and bool((a == tot).all() and (b == tot).all() and (c == 10 * tot).all())
         # column Linf: MAX
         part = torch.from_numpy(o.reduce(full[r0:r1], apply=1, main_op="abs", reduce_op="max"))
         D.combine_partials(part, "max")
