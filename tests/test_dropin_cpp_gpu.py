@@ -47,3 +47,26 @@ def test_multi_device_layer(cuda):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([binary], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "ALL PASSED" in r.stdout, r.stdout[-4000:]
+
+
+def _run_snmg(name):
+    binary = os.path.join(HERE, "cpp", name)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([binary], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "SNMG ALL PASSED" in r.stdout, r.stdout[-4000:]
+    assert "FAIL" not in r.stdout
+
+
+def test_sharded_overloads_standalone(cuda):
+    """raft::linalg::reduce / reduce_rows_by_key taking a raft::device_resources_snmg and one view per device
+    (include/raft/linalg/sharded_reduce.cuh), stand-alone build, on every visible device: tests/cpp/test_snmg.cu."""
+    assert os.path.exists(os.path.join(HERE, "cpp", "test_snmg")), "build it with `make -C tests/cpp`"
+    _run_snmg("test_snmg")
+
+
+def test_sharded_overloads_on_the_reference_core(cuda):
+    """The same program compiled against the reference's own raft/core: resources.hpp, the MULTI_GPU and
+    NCCL_COMM resources (core/resource/multi_gpu.hpp, nccl_comm.hpp)."""
+    if not os.path.exists(os.path.join(HERE, "cpp", "test_snmg_overlay")):
+        pytest.skip("overlay build needs the reference checkout at build time")
+    _run_snmg("test_snmg_overlay")
