@@ -70,6 +70,63 @@ B2R_DI void push_element(GenericState<KeyValue<K, V>, op::ArgMax>& st, const V& 
   st.v.key        = take ? k : st.v.key;
 }
 
+// Row argmin / argmax of tagged values in the one-pass kernels: a lane walks ITS elements of a row in
+// ascending column order, so among them "strictly better" alone keeps the first best one - one compare and two
+// selects per element instead of three compares. To stay exactly argmin_op(init, elements) the lanes do not
+// start from `init` but from {largest key, init.value}: nothing but a strictly better value replaces that,
+// a walk that found none looks once more for elements EQUAL to init.value (they win the tie against the largest
+// key, the first of them having the lowest column), the cross-lane merges use the full rule, and the writer
+// folds the caller's `init` in last. NaN elements are never taken, as with the full rule.
+template <typename State, typename MainOp, typename ReduceOp>
+struct kvp_walk : std::false_type {};
+template <typename K, typename V>
+struct kvp_walk<GenericState<KeyValue<K, V>, op::ArgMin>, op::ToKeyValue<K>, op::ArgMin> : std::true_type {
+  static constexpr bool is_min = true;
+};
+template <typename K, typename V>
+struct kvp_walk<GenericState<KeyValue<K, V>, op::ArgMax>, op::ToKeyValue<K>, op::ArgMax> : std::true_type {
+  static constexpr bool is_min = false;
+};
+template <typename K>
+B2R_DI constexpr K kvp_largest_key()
+{
+  return K(~K(0)) > K(0) ? K(~K(0)) : K((unsigned long long)(~0ull) >> (65 - 8 * sizeof(K)));
+}
+
+// The U x CPL vectors a lane holds of U rows (chunks lig, lig + G, ... of each), walked in column order.
+template <bool IsMin, typename K, typename V, typename InT, int VEC, int U, int CPL>
+B2R_DI void kvp_walk_rows(GenericState<KeyValue<K, V>, typename std::conditional<IsMin, op::ArgMin, op::ArgMax>::type> (&st)[U],
+                          const VecOf<InT, VEC> (&v)[U][CPL], int first_col, int chunk_stride_cols, V start)
+{
+  constexpr K kLast = kvp_largest_key<K>();
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    V bv = start;
+    K bk = kLast;
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const V x       = V(v[u][k].e[e]);
+        const bool take = IsMin ? (x < bv) : (x > bv);
+        bv              = take ? x : bv;
+        bk              = take ? K(first_col + k * chunk_stride_cols + e) : bk;
+      }
+    }
+    if (bk == kLast) {  // nothing beat the start value: elements equal to it still beat the largest key
+#pragma unroll
+      for (int k = CPL - 1; k >= 0; --k) {
+#pragma unroll
+        for (int e = VEC - 1; e >= 0; --e) {
+          if (V(v[u][k].e[e]) == bv) bk = K(first_col + k * chunk_stride_cols + e);
+        }
+      }
+    }
+    st[u].v.key   = bk;
+    st[u].v.value = bv;
+  }
+}
+
 template <typename InT,
           typename OutT,
           typename IdxT,
@@ -128,9 +185,16 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
       const InT* base    = data + (valid > 0 ? row0 : n_rows - 1) * ld;
       const int64_t step = valid > 0 ? int64_t(gpw) * ld : 0;
       State st[U];
+      constexpr bool kWalk = kvp_walk<State, MainOp, ReduceOp>::value;
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        init_state<OutT, State, isSum>(st[u], init, lig == 0);
+      for (int u = 0; u < U; ++u) {
+        if constexpr (kWalk) {
+          st[u].v.key   = kvp_largest_key<decltype(st[u].v.key)>();
+          st[u].v.value = init.value;
+        } else {
+          init_state<OutT, State, isSum>(st[u], init, lig == 0);
+        }
+      }
       // CPL chunks of every row per lane and pass: U * CPL loads are in flight per lane, and the
       // more of a row one lane sums by itself the fewer exchanges the reduction below needs
       // (the pass structure is the same for every lane of the warp - a pass is "full" only if it is for
@@ -149,13 +213,30 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
             for (int k = 0; k < CPL; ++k)
               v[u][k] = load_stream<InT, VEC>(base + u * step + int64_t(c0 + k * G) * VEC);
           }
+          if constexpr (kWalk) {
+            if (cb == 0) {
+              // the row's first (for one-pass rows: only) pass: the lane's own columns in ascending order
+              kvp_walk_rows<kvp_walk<State, MainOp, ReduceOp>::is_min>(st, v, c0 * VEC, G * VEC, init.value);
+            } else {
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
+              for (int u = 0; u < U; ++u) {
 #pragma unroll
-            for (int k = 0; k < CPL; ++k) {
+                for (int k = 0; k < CPL; ++k) {
 #pragma unroll
-              for (int e = 0; e < VEC; ++e)
-                push_element<OutT, IdxT>(st[u], v[u][k].e[e], (c0 + k * G) * VEC + e, main_op, reduce_op);
+                  for (int e = 0; e < VEC; ++e)
+                    push_element<OutT, IdxT>(st[u], v[u][k].e[e], (c0 + k * G) * VEC + e, main_op, reduce_op);
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+#pragma unroll
+              for (int k = 0; k < CPL; ++k) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                  push_element<OutT, IdxT>(st[u], v[u][k].e[e], (c0 + k * G) * VEC + e, main_op, reduce_op);
+              }
             }
           }
         } else {
@@ -193,6 +274,7 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
             const int64_t r = row0 + int64_t(slot) * gpw;
             if (r < n_rows) {
               OutT v = st[i].value();
+              if constexpr (kWalk) v = reduce_op(init, v);  // the lanes started from {largest key, init.value}
               if constexpr (std::is_same<StoreT, OutT>::value) {
                 if (inplace) v = reduce_op(out[r], v);
               }

@@ -148,9 +148,16 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
       const int slots = (left + gpw - 1) >> gsh;
       const int valid = left <= 0 ? 0 : (slots < U ? slots : U);
       State st[U];
+      constexpr bool kWalk = kvp_walk<State, MainOp, ReduceOp>::value;  // see row_reduce.cuh
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        init_state<OutT, State, isSum>(st[u], init, lig == 0);
+      for (int u = 0; u < U; ++u) {
+        if constexpr (kWalk) {
+          st[u].v.key   = kvp_largest_key<decltype(st[u].v.key)>();
+          st[u].v.value = init.value;
+        } else {
+          init_state<OutT, State, isSum>(st[u], init, lig == 0);
+        }
+      }
       Vec v[U][CPL];
       if (valid == U && exact) {
         const unsigned char* base = tile + unsigned(lrow0) * row_bytes + unsigned(lig) * unsigned(sizeof(Vec));
@@ -160,13 +167,17 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
           for (int k = 0; k < CPL; ++k)
             v[u][k] = *reinterpret_cast<const Vec*>(base + u * step_full + unsigned(k * G) * unsigned(sizeof(Vec)));
         }
+        if constexpr (kWalk) {
+          kvp_walk_rows<kvp_walk<State, MainOp, ReduceOp>::is_min>(st, v, lig * VEC, G * VEC, init.value);
+        } else {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
+          for (int u = 0; u < U; ++u) {
 #pragma unroll
-          for (int k = 0; k < CPL; ++k) {
+            for (int k = 0; k < CPL; ++k) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e)
-              push_element<OutT, IdxT>(st[u], v[u][k].e[e], (lig + k * G) * VEC + e, main_op, reduce_op);
+              for (int e = 0; e < VEC; ++e)
+                push_element<OutT, IdxT>(st[u], v[u][k].e[e], (lig + k * G) * VEC + e, main_op, reduce_op);
+            }
           }
         }
       } else {
@@ -206,6 +217,7 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
             if (lr < nr) {
               const int64_t r = tile_row0 + lr;
               OutT val        = st[i].value();
+              if constexpr (kWalk) val = reduce_op(init, val);  // the lanes started from {largest key, init.value}
               if constexpr (std::is_same<StoreT, OutT>::value) {
                 if (inplace) val = reduce_op(out[r], val);
               }

@@ -168,6 +168,35 @@ def test_kvp_grid(cuda, oracle, in_dt, rows, cols, op):
     assert np.array_equal(kv0.values.cpu().numpy().astype(np.float64), ev2)
 
 
+@pytest.mark.parametrize("cols", [4, 16, 64, 128, 100, 1024, 3000])
+@pytest.mark.parametrize("op", ["argmin", "argmax"])
+@pytest.mark.parametrize("ring", [False, True])
+def test_kvp_ties_with_the_start_value(cuda, oracle, knobs, cols, op, ring):
+    """argmin_op / argmax_op are exact folds over {init, elements} (core/operators.hpp:187-203): an element EQUAL
+    to init.value wins only with a lower key than init.key, NaN elements never win, and a row that holds nothing
+    better keeps the start pair. The one-pass kernels walk a lane's elements with a strict compare and settle
+    these cases afterwards; every one of them is checked against the oracle here, for start keys below, inside
+    and above the columns, on the direct kernels and on the ring kernel."""
+    if ring:
+        knobs(B2R_ROW_TMA="1")
+    rows = 6000
+    best = 0.0 if op == "argmin" else 9.0
+    t, host = device_synth((rows, cols), np.float32, 77, "int", 0, 10, cuda)
+    host = host.copy()
+    host[0::7] = 5.0                 # whole rows equal to the start value used below
+    host[1::7] = np.inf if op == "argmin" else -np.inf   # nothing can beat an infinite start value
+    host[2::7, : cols // 2] = np.nan   # NaN never wins
+    host[3::7] = np.nan              # a row of NaN keeps the start pair
+    host[4::7, cols - 1] = best      # the best value in the last column only
+    t.copy_(torch.from_numpy(host))
+    for init, init_key in ((5.0, 0), (5.0, cols // 2), (5.0, 10 * cols), (np.inf if op == "argmin" else -np.inf, 3),
+                           (np.inf if op == "argmin" else -np.inf, 2 ** 31 - 1), (best, 1)):
+        kv = linalg.reduce(t, linalg.ALONG_ROWS, main_op="to_kvp", reduce_op=op, init=init, init_key=init_key)
+        ek, ev = oracle.reduce(host, main_op="to_kvp", reduce_op=op, init=init, init_key=init_key)
+        assert np.array_equal(kv.keys.cpu().numpy().astype(np.int64), ek), (init, init_key)
+        assert np.array_equal(kv.values.cpu().numpy().astype(np.float64), ev, equal_nan=True), (init, init_key)
+
+
 def test_kvp_column_major_and_strided_refusal(cuda, oracle):
     t, host = device_synth((300, 40), np.float32, 8, "int", 0, 4, cuda)
     cm = as_layout(t, 1)
