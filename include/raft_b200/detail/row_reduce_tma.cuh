@@ -239,5 +239,199 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
   }
 }
 
+// Few, very long rows (the "thick" case of the reference, coalesced_reduction-inl.cuh:481-533, and the
+// full-array reductions built on it): a row is cut into segments, one CTA per (segment, row) as in
+// row_split_kernel, but the segment comes through a ring of 32 KB bulk copies and the 256 consumers sum
+// straight out of shared memory - a CTA keeps 128 KB in flight without a register, which is what lets a
+// pure read run at 7.2-7.3 TB/s on this part where 16-byte loads stop at 6.3-6.5. The segment's partial
+// goes to partial[row * n_seg + seg] (row_finalize_kernel folds them), or straight to `out` when the row
+// has one segment. A row length that is no multiple of the vector: the last segment's consumers take the tail
+// from global memory. Waits are bounded as everywhere (col_reduce_tma.cuh).
+template <typename InT,
+          typename OutT,
+          typename IdxT,
+          typename MainOp,
+          typename ReduceOp,
+          typename FinalOp,
+          int VEC,
+          typename StoreT = OutT>
+__global__ void __launch_bounds__(kTmaThreads, 1)
+  row_split_ring_kernel(StoreT* __restrict__ out,
+                        typename state_for<OutT, ReduceOp>::type::carry_t* __restrict__ partial,
+                        const InT* __restrict__ data,
+                        int64_t n_rows,
+                        int64_t row_len,
+                        int64_t ld,
+                        OutT init,
+                        bool inplace,
+                        MainOp main_op,
+                        ReduceOp reduce_op,
+                        FinalOp final_op,
+                        int64_t seg_vecs,
+                        int tile_vecs,
+                        int STAGES,
+                        RingCtl ctl)
+{
+  using State          = typename state_for<OutT, ReduceOp>::type;
+  using Vec            = VecOf<InT, VEC>;
+  constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  extern __shared__ __align__(128) unsigned char smem_tma[];
+  __shared__ __align__(8) uint64_t s_full[kTmaMaxStages];
+  __shared__ __align__(8) uint64_t s_empty[kTmaMaxStages];
+  __shared__ int s_abort;
+  __shared__ State s_warp[kTmaConsumers / 32];
+
+  const int tid        = threadIdx.x;
+  const bool producer  = tid >= kTmaConsumers;
+  const int n_seg      = gridDim.x;
+  const int seg        = blockIdx.x;
+  const int64_t nvec   = row_len / VEC;
+  const int64_t v0     = int64_t(seg) * seg_vecs;
+  int64_t v1           = v0 + seg_vecs;
+  v1                   = v1 < nvec ? v1 : nvec;
+  const int64_t n_v    = v1 > v0 ? v1 - v0 : 0;
+  const int tiles_row  = int((n_v + tile_vecs - 1) / tile_vecs);  // tiles of one row's segment
+  const bool direct    = n_seg == 1;
+  const size_t stage_stride = size_t(tile_vecs) * sizeof(Vec);
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], kTmaConsumers / 32);
+    }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  volatile int* abort_flag = &s_abort;
+
+  if (producer) {
+    if (tid == kTmaConsumers) {
+      long long issued = 0;
+      bool alive       = true;
+      for (int64_t row = blockIdx.y; row < n_rows && alive; row += gridDim.y) {
+        const Vec* rp = reinterpret_cast<const Vec*>(data + row * ld) + v0;
+        for (int t = 0; t < tiles_row; ++t) {
+          const int s          = int(issued % STAGES);
+          const unsigned phase = unsigned(issued / STAGES) & 1u;
+          if (!mbar_wait_bounded(&s_empty[s], phase ^ 1u, abort_flag, ctl.limit_ns)) {
+            alive = false;
+            break;
+          }
+          if (issued == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) {  // test hook: never requested
+            ++issued;
+            continue;
+          }
+          const int64_t left = n_v - int64_t(t) * tile_vecs;
+          const unsigned nb  = unsigned((left < tile_vecs ? left : tile_vecs) * int64_t(sizeof(Vec)));
+          mbar_expect_tx(&s_full[s], nb);
+          bulk_load(smem_tma + s * stage_stride, rp + int64_t(t) * tile_vecs, nb, &s_full[s]);
+          ++issued;
+        }
+      }
+      if (alive) producer_wait_released(s_empty, issued, STAGES, abort_flag, ctl.limit_ns);
+      if (*abort_flag != 0) {
+        const long long first = issued > STAGES ? issued - STAGES : 0;
+        for (long long t = first; t < issued; ++t) {
+          if (t == ctl.skip_tile && blockIdx.x == 0 && blockIdx.y == 0) continue;
+          mbar_drain_bounded(&s_full[t % STAGES], unsigned(t / STAGES) & 1u, ctl.limit_ns);
+        }
+        ring_report_timeout(ctl);
+      }
+    }
+    return;
+  }
+
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  long long seq  = 0;
+  bool dead      = false;
+  for (int64_t row = blockIdx.y; row < n_rows; row += gridDim.y) {
+    constexpr int U = 4;
+    State st[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      init_state<OutT, State, isSum>(st[u], init, direct && tid == 0 && u == 0);
+    for (int t = 0; t < tiles_row; ++t, ++seq) {
+      if (dead) continue;
+      const int s          = int(seq % STAGES);
+      const unsigned phase = unsigned(seq / STAGES) & 1u;
+      if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) {
+        dead = true;
+        continue;
+      }
+      const Vec* tile    = reinterpret_cast<const Vec*>(smem_tma + s * stage_stride);
+      const int64_t base = v0 + int64_t(t) * tile_vecs;  // vector index of the tile's first vector in the row
+      const int64_t left = n_v - int64_t(t) * tile_vecs;
+      const int nt       = int(left < tile_vecs ? left : tile_vecs);
+      int c              = tid;
+      for (; c + (U - 1) * kTmaConsumers < nt; c += U * kTmaConsumers) {
+        Vec v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          v[u] = tile[c + u * kTmaConsumers];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            st[u].push(OutT(main_op(v[u].e[e], IdxT((base + c + u * kTmaConsumers) * VEC + e))), reduce_op);
+        }
+      }
+      for (; c < nt; c += kTmaConsumers) {
+        const Vec v = tile[c];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          st[0].push(OutT(main_op(v.e[e], IdxT((base + c) * VEC + e))), reduce_op);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+    }
+    if constexpr (VEC > 1) {
+      // a row length that is no multiple of the vector width: the last segment takes the tail
+      if (seg == n_seg - 1) {
+        const InT* rp = data + row * ld;
+        for (int64_t i = nvec * VEC + tid; i < row_len; i += kTmaConsumers)
+          st[0].push(OutT(main_op(rp[i], IdxT(i))), reduce_op);
+      }
+    }
+#pragma unroll
+    for (int u = 1; u < U; ++u)
+      st[0].merge(st[u], reduce_op);
+    // the 8 consumer warps meet (named barrier: the producer warp is not part of it)
+    State r = st[0];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      State got = shfl_xor_any(r, off);
+      r.merge(got, reduce_op);
+    }
+    if (lane == 0) s_warp[warp] = r;
+    asm volatile("bar.sync 1, %0;" ::"n"(kTmaConsumers) : "memory");
+    if (tid == 0) {
+      State tot = s_warp[0];
+      for (int w = 1; w < kTmaConsumers / 32; ++w)
+        tot.merge(s_warp[w], reduce_op);
+      const bool failed = *abort_flag != 0;
+      if (direct) {
+        OutT val = tot.value();
+        if constexpr (std::is_same<StoreT, OutT>::value) {
+          if (inplace) val = reduce_op(out[row], val);
+        }
+        StoreT res = final_op(val);
+        if constexpr (std::is_floating_point<StoreT>::value) {
+          if (failed) res = StoreT(NAN);
+        }
+        out[row] = res;
+      } else {
+        auto carry = tot.carry();
+        if constexpr (std::is_floating_point<decltype(carry)>::value) {
+          if (failed) carry = decltype(carry)(NAN);
+        }
+        partial[row * n_seg + seg] = carry;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kTmaConsumers) : "memory");  // s_warp is reused by the next row
+  }
+}
+
 }  // namespace detail
 }  // namespace raft_b200

@@ -90,6 +90,43 @@ def test_reduce_split_rows(cuda, oracle, rows, cols):
     assert np.array_equal(kv.keys.cpu().numpy(), host.argmin(axis=1))
 
 
+# a handful of very long rows: the ring form of the split (segments of a row come through 32 KB bulk copies);
+# the threshold is lowered so that ragged lengths, tails shorter than a vector and a last segment of a few
+# vectors are all seen at sizes the oracle finishes quickly, then one case at the default threshold
+@pytest.mark.parametrize("rows,cols", [(1, 5_000_000), (2, 1_000_003), (3, 262144 + 4), (7, 300_001), (16, 2048 * 148)])
+@pytest.mark.parametrize("in_dt", [np.float32, np.float64, np.float16])
+def test_reduce_split_rows_ring(cuda, oracle, knobs, rows, cols, in_dt):
+    knobs(B2R_ROW_SPLIT_RING_MB="1")
+    t, host = device_synth((rows, cols), in_dt, 77, "uniform", -1, 1, cuda)
+    tol = {np.float32: 1e-5, np.float64: 1e-10, np.float16: 1e-5}[in_dt]
+    got = linalg.reduce(t, linalg.ALONG_ROWS, out_dtype=torch.float32 if in_dt == np.float16 else None)
+    oracle.assert_approx(oracle.reduce(host), got.cpu().numpy(), tol)
+    knobs(B2R_ROW_SPLIT_RING="2")
+    plain = linalg.reduce(t, linalg.ALONG_ROWS, out_dtype=torch.float32 if in_dt == np.float16 else None)
+    oracle.assert_approx(plain.cpu().numpy().astype(np.float64), got.cpu().numpy(), tol)
+    knobs(B2R_ROW_SPLIT_RING=None)
+    if in_dt == np.float16:
+        return
+    prev = got.cpu().numpy().astype(np.float64)
+    linalg.reduce(t, linalg.ALONG_ROWS, got, inplace=True, main_op="sq", final_op="sqrt")
+    oracle.assert_approx(oracle.reduce(host, main_op="sq", final_op="sqrt", inplace=True, prev_val=prev),
+                         got.cpu().numpy(), 10 * tol)
+    got = linalg.reduce(t, linalg.ALONG_ROWS, main_op="abs", reduce_op="max")
+    assert np.array_equal(got.cpu().numpy(), np.abs(host).max(axis=1))
+    if in_dt == np.float32:
+        kv = linalg.reduce(t, linalg.ALONG_ROWS, main_op="to_kvp", reduce_op="argmin", init=float("inf"))
+        assert np.array_equal(kv.keys.cpu().numpy(), host.argmin(axis=1))
+        assert np.array_equal(kv.values.cpu().numpy(), host.min(axis=1))
+
+
+def test_reduce_split_rows_ring_default_threshold(cuda, oracle):
+    t, host = device_synth((2, (1 << 24) + 5), np.float32, 5, "uniform", -1, 1, cuda)  # 64 MiB + 20 B per row
+    got = linalg.reduce(t, linalg.ALONG_ROWS, main_op="sq", final_op="sqrt")
+    oracle.assert_approx(oracle.reduce(host, main_op="sq", final_op="sqrt"), got.cpu().numpy(), 1e-5)
+    ones = torch.ones((1, 1 << 26), dtype=torch.float32, device=cuda)
+    assert linalg.reduce(ones, linalg.ALONG_ROWS).item() == float(1 << 26)
+
+
 # cpp/tests/linalg/coalesced_reduction.cu:109-139
 @pytest.mark.parametrize("rows,cols,tol32,tol64", [(r, c, 2e-6, 1e-9) for r in (50, 10000)
                                                    for c in (2, 3, 7, 9, 20, 55, 100, 270)] + [(10, 25000, 1e-4, 1e-7)])

@@ -62,6 +62,14 @@ def test_row_ring_key_value_output_reports_through_the_status(cuda, knobs):
                             or pytest.fail("argmin wrong"))
 
 
+def test_split_row_ring(cuda, knobs):
+    t = torch.ones((2, 1 << 22), dtype=torch.float32, device=cuda)
+    _expect_timeout_then_ok(cuda, knobs, {"B2R_ROW_SPLIT_RING_MB": "1"}, lambda: linalg.reduce(t, linalg.ALONG_ROWS),
+                            lambda o: (torch.isnan(o[0]).item() and not torch.isnan(o[1]).item())
+                            or pytest.fail("unfinished row not NaN"),
+                            lambda o: torch.all(o == float(1 << 22)).item() or pytest.fail("row sums wrong"))
+
+
 def test_staged_rows_off_16_byte_boundaries(cuda, knobs):
     t = torch.ones((400000, 31), dtype=torch.float32, device=cuda)
     _expect_timeout_then_ok(cuda, knobs, {"B2R_ROW_STAGED_MIN_KB": "1024"}, lambda: linalg.reduce(t, linalg.ALONG_ROWS),
