@@ -119,6 +119,7 @@ struct Tuning {
   int split_ctas_per_sm    = 4;   // B2R_SPLIT_CPS
   int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
+  int key_unit_rows        = 0;     // B2R_KEY_UNIT_ROWS rows of one key a warp sums into one partial row (0: by size, 128..384)
   int key_algo             = 0;     // B2R_KEY_ALGO   0: by size, 1: shared-memory table, 2: sort then stream, 3: one-launch kernel (<= 32768 rows)
   int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted tiles, a lane per segment, 3: sorted tiles, a warp walking its keys
   int colkey32_ch          = 0;     // B2R_COLKEY32_CH columns per chunk of the walk form of the keyed column sums (0: the longest that fits)
@@ -169,6 +170,7 @@ inline Tuning read_tuning_from_env()
   x.split_ctas_per_sm    = env_int("B2R_SPLIT_CPS", x.split_ctas_per_sm);
   x.key_block_rows       = env_int("B2R_KEY_BLOCK", x.key_block_rows);
   x.key_window_rows      = env_int("B2R_KEY_WINDOW", x.key_window_rows);
+  x.key_unit_rows        = env_int("B2R_KEY_UNIT_ROWS", x.key_unit_rows);
   x.key_algo             = env_int("B2R_KEY_ALGO", x.key_algo);
   x.colkey_algo          = env_int("B2R_COLKEY_ALGO", x.colkey_algo);
   x.colkey32_ch          = env_int("B2R_COLKEY32_CH", x.colkey32_ch);

@@ -1,17 +1,16 @@
 // Keyed row sums, "sort then stream" formulation:
 //     sums[keys[i]][:] += w[i] * A[i][:]
 //
-// Six kernels, no floating-point atomics, every matrix row read from HBM once:
+// Five kernels, no floating-point atomics, every matrix row read from HBM once:
 //
 //  rbk_sort_kernel     one CTA per window of W consecutive rows (W <= 65536, sized so that the
 //                      windows fill whole waves of resident CTAs). Counting sort of the window's row
 //                      offsets by key with integer shared-memory atomics: perm[window][.] (16-bit
 //                      offsets staged in shared memory, written out coalesced) and offs[window][k].
-//  rbk_count_kernel    rows of every key in every GROUP of consecutive windows. The group size is
-//                      chosen so that a key has about kUnitTarget rows per group, whatever the
-//                      number of keys (1 window for up to ~400 keys, 32 for 8192 and more).
-//  rbk_units_kernel    one CTA per group: prefix sum over the keys -> the work units (at most
-//                      kUnitCap rows of one key each, split evenly) and the list of (group, key)
+//  rbk_units_kernel    one CTA per GROUP of consecutive windows (the group size is chosen so that a key
+//                      has about kUnitTarget rows per group, whatever the number of keys): rows of every
+//                      key in the group, prefix sum over the keys -> the work units (at most
+//                      1.5 x that many rows of one key each, split evenly) and the list of (group, key)
 //                      pairs that got more than one unit.
 //  rbk_stream_kernel   one warp per work unit, units handed out dynamically: the warp finds the
 //                      unit's rows through the sorted windows (a search over at most 32 segment
@@ -39,11 +38,24 @@
 namespace raft_b200 {
 namespace detail {
 
-constexpr int kUnitTarget  = 128;    // rows per work unit aimed for
-constexpr int kUnitCap     = 192;    // rows per work unit at most
+constexpr int kUnitTarget  = 128;    // rows per work unit aimed for, at least (B2R_KEY_UNIT_ROWS sets it)
 constexpr int kMaxGroup    = 32;     // windows per group at most (one lane per window)
 constexpr int kSortTpb     = 1024;
 constexpr int kMaxSortKeys = 24576;  // histogram + cursors (8 bytes per key) must fit shared memory
+
+// Rows of one key that a warp sums into one partial row. Every unit costs a 8-byte-per-column partial row that is
+// written and read once more, so long units save traffic (10^7 x 128, 1024 keys: 128 rows 760 + 25 us in the
+// stream and merge kernels, 384 rows 746 + 16); short ones keep enough units per resident warp for the queue to
+// level the warps out at the end. Eight units per resident warp, between 128 and 384 rows.
+inline int rbk_unit_target(int64_t nrows)
+{
+  const int knob = tuning().key_unit_rows;
+  if (knob >= 16 && knob <= 4096) return knob;
+  int64_t t = nrows / (int64_t(sm_count()) * 24 * 8);
+  t         = t / 32 * 32;
+  return int(t < kUnitTarget ? kUnitTarget : (t > 384 ? 384 : t));
+}
+inline int rbk_unit_cap(int64_t nrows) { return rbk_unit_target(nrows) * 3 / 2; }  // rows per work unit at most
 
 struct SortedPlan {
   int vec;
@@ -163,39 +175,21 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
   }
 }
 
-// gcnt[g][k] = rows of key k in the windows of group g.
-__global__ void __launch_bounds__(256) rbk_count_kernel(const int* __restrict__ offs,
-                                                       int nkeys,
-                                                       int n_windows,
-                                                       int group,
-                                                       int n_groups,
-                                                       int* __restrict__ gcnt)
-{
-  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
-  if (idx >= int64_t(n_groups) * nkeys) return;
-  const int g  = int(idx / nkeys);
-  const int k  = int(idx - int64_t(g) * nkeys);
-  const int w0 = g * group;
-  int nw       = n_windows - w0;
-  nw           = nw < group ? nw : group;
-  int t        = 0;
-  for (int w = 0; w < nw; ++w) {
-    const int* wo = offs + size_t(w0 + w) * (nkeys + 1);
-    t += wo[k + 1] - wo[k];
-  }
-  gcnt[idx] = t;
-}
-
-// One CTA per group. From gcnt[g][.], keys taken TPB at a time so that loads and stores coalesce:
+// One CTA per group, keys taken TPB at a time so that loads and stores coalesce. First the rows of every key in
+// the group's windows, gcnt[g][k] (the merge adds them up to the exact row counts), then from them:
 //   uoffs[g][nkeys + 1]            first work unit of each key
 //   ukey / ufirst / ulen [max_units]  per unit: key, ordinal of its first row among the key's rows
 //                                  of the group, and row count (an even split into
-//                                  ceil(rows / kUnitCap) units)
+//                                  ceil(rows / unit_cap) units)
 //   fold_list                      (g * nkeys + k) of every key that got more than one unit
 template <int TPB>
-__global__ void __launch_bounds__(TPB) rbk_units_kernel(const int* __restrict__ gcnt,
+__global__ void __launch_bounds__(TPB) rbk_units_kernel(const int* __restrict__ offs,
+                                                       int n_windows,
+                                                       int group,
+                                                       int* __restrict__ gcnt,
                                                        int nkeys,
                                                        int max_units,
+                                                       int unit_cap,
                                                        int* __restrict__ uoffs,
                                                        int* __restrict__ ukey,
                                                        int* __restrict__ ufirst,
@@ -210,7 +204,10 @@ __global__ void __launch_bounds__(TPB) rbk_units_kernel(const int* __restrict__ 
   const int tid  = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int* cnt = gcnt + size_t(g) * nkeys;
+  int* cnt       = gcnt + size_t(g) * nkeys;
+  const int w0   = g * group;
+  int nw         = n_windows - w0;
+  nw             = nw < group ? nw : group;
   int* g_uoffs   = uoffs + size_t(g) * (nkeys + 1);
   int* g_ukey    = ukey + size_t(g) * max_units;
   int* g_ufirst  = ufirst + size_t(g) * max_units;
@@ -219,8 +216,15 @@ __global__ void __launch_bounds__(TPB) rbk_units_kernel(const int* __restrict__ 
   int run = 0;  // units of the keys before this tile
   for (int k0 = 0; k0 < nkeys; k0 += TPB) {
     const int k  = k0 + tid;
-    const int t  = k < nkeys ? cnt[k] : 0;
-    const int nu = (t + kUnitCap - 1) / kUnitCap;
+    int t        = 0;
+    if (k < nkeys) {
+      const int* wo = offs + size_t(w0) * (nkeys + 1) + k;
+#pragma unroll 8
+      for (int w = 0; w < nw; ++w)
+        t += wo[size_t(w) * (nkeys + 1) + 1] - wo[size_t(w) * (nkeys + 1)];
+      cnt[k] = t;
+    }
+    const int nu = (t + unit_cap - 1) / unit_cap;
     int inc      = nu;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -386,9 +390,14 @@ __global__ void __launch_bounds__(256, 3) rbk_stream_kernel(typename sum_state<S
         }
       };
       if (G >= 8) {  // Q * gpw divides 32: translate 32 rows, then hand them out
+        // the look-up of the NEXT 32 rows is issued before the loads of these 32, so that its latency (a
+        // dependent read of the sorted list) is hidden behind them instead of leaving the warp without a
+        // load in flight once per batch
+        unsigned next_row = translate(lane);
         for (int tb = 0; tb < len; tb += 32) {
-          const unsigned my_row = translate(tb + lane);
-          const int nb          = len - tb < 32 ? len - tb : 32;
+          const unsigned my_row = next_row;
+          if (tb + 32 < len) next_row = translate(tb + 32 + lane);
+          const int nb = len - tb < 32 ? len - tb : 32;
           for (int i0 = 0; i0 < nb; i0 += Q * gpw)
             pass(i0, nb, [&](int k) { return __shfl_sync(0xffffffffu, my_row, i0 + k * gpw + grp); });
         }
@@ -476,14 +485,13 @@ __global__ void __launch_bounds__(256) rbk_fold_kernel(typename sum_state<SumT>:
 // groups s, s + WPK, ... (one row per group after rbk_fold_kernel), four loaded before any is
 // consumed, and the WPK partial results are added in warp order through shared memory: the order
 // of the additions is fixed.
-// Warp 0 of the key also adds up the key's row count from the sort offsets of all windows.
+// The last warp of the key also adds up the key's exact row count from the per-group counts.
 template <typename SumT, int WPK>
 __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
                                                        long long* __restrict__ counts,
                                                        const typename sum_state<SumT>::type::carry_t* __restrict__ partial,
-                                                       const int* __restrict__ offs,
+                                                       const int* __restrict__ gcnt,
                                                        const int* __restrict__ uoffs,
-                                                       int n_windows,
                                                        int n_groups,
                                                        int max_units,
                                                        int ncols,
@@ -501,12 +509,10 @@ __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
   const int k      = WPK > 1 ? int(blockIdx.x) : int(blockIdx.x) * 8 + warp;
   const bool valid = k < nkeys;  // uniform per CTA when WPK > 1, so the barriers below are safe
 
-  if (valid && sub == 0 && counts != nullptr) {
+  if (valid && sub == WPK - 1 && counts != nullptr) {  // the warp that has the fewest groups to fold
     long long n = 0;
-    for (int w = lane; w < n_windows; w += 32) {
-      const int* wo = offs + size_t(w) * (nkeys + 1);
-      n += wo[k + 1] - wo[k];
-    }
+    for (int g = lane; g < n_groups; g += 32)
+      n += gcnt[size_t(g) * nkeys + k];
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1)
       n += __shfl_xor_sync(0xffffffffu, n, off);
@@ -620,7 +626,7 @@ inline SortedPlan plan_rows_by_key_sorted(const DataT* A, int64_t lda, int64_t n
   p.window_rows      = int(W);
   p.n_windows        = int(ceil_div<int64_t>(nrows, W));
   // windows per group: a key should own about kUnitTarget rows of a group
-  int64_t group = (int64_t(kUnitTarget) * nkeys + W / 2) / W;
+  int64_t group = (int64_t(rbk_unit_target(nrows)) * nkeys + W / 2) / W;
   if (group > kMaxGroup) group = kMaxGroup;
   if (group > p.n_windows) group = p.n_windows;
   if (group < 1) group = 1;
@@ -630,8 +636,8 @@ inline SortedPlan plan_rows_by_key_sorted(const DataT* A, int64_t lda, int64_t n
   const int64_t rows_in_group = nrows < group_rows ? nrows : group_rows;
   // every key present adds at most one ragged unit on top of the full ones
   const int64_t present = nkeys < rows_in_group ? nkeys : rows_in_group;
-  p.max_units           = int(present + rows_in_group / kUnitCap + 1);
-  const int64_t heavy   = rows_in_group / kUnitCap + 1;  // keys with more than kUnitCap rows in a group
+  p.max_units           = int(present + rows_in_group / rbk_unit_cap(nrows) + 1);
+  const int64_t heavy   = rows_in_group / rbk_unit_cap(nrows) + 1;  // keys with more than a unit's rows in a group
   p.max_fold            = int(int64_t(p.n_groups) * (heavy < nkeys ? heavy : nkeys));
   const size_t per_key  = size_t(nkeys + 1) * sizeof(int);
   const size_t per_unit = size_t(p.n_groups) * p.max_units * sizeof(int);
@@ -714,11 +720,9 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
-  // 2. rows per (group, key); 3. unit tables and the list of keys to fold
-  const int64_t gk = int64_t(p.n_groups) * nkeys;
-  rbk_count_kernel<<<unsigned(ceil_div<int64_t>(gk, 256)), 256, 0, stream>>>(offs, nk, p.n_windows, p.group,
-                                                                             p.n_groups, gcnt);
-  rbk_units_kernel<1024><<<unsigned(p.n_groups), 1024, 0, stream>>>(gcnt, nk, p.max_units, uoffs, ukey, ufirst, ulen,
+  // 2. rows per (group, key), unit tables and the list of keys to fold
+  rbk_units_kernel<1024><<<unsigned(p.n_groups), 1024, 0, stream>>>(offs, p.n_windows, p.group, gcnt, nk, p.max_units,
+                                                                    rbk_unit_cap(nrows), uoffs, ukey, ufirst, ulen,
                                                                     fold_list, counter + 1);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -735,7 +739,7 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
     static int occ = resident_ctas(kern, 256, 0);                                                            \
     int64_t ctas   = int64_t(sms) * occ;                                                                     \
     /* about four items per resident warp: cut the columns when the rows alone give fewer */                \
-    const int64_t est_units = ceil_div<int64_t>(nrows, kUnitTarget);                                         \
+    const int64_t est_units = ceil_div<int64_t>(nrows, rbk_unit_target(nrows));                                        \
     int64_t split           = ceil_div<int64_t>(ctas * 8 * 4, est_units);                                    \
     if (split > passes) split = passes;                                                                      \
     while (split > 1 && slots * split >= (int64_t(1) << 30))                                                 \
@@ -763,10 +767,10 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
                                                                  int(ncols), nk);
   if (nkeys <= 2048) {  // few keys: a CTA per key
     rbk_merge_kernel<SumT, 8><<<unsigned(nkeys), 256, 0, stream>>>(
-      sums, counts, partial, offs, uoffs, p.n_windows, p.n_groups, p.max_units, int(ncols), nk, reset);
+      sums, counts, partial, gcnt, uoffs, p.n_groups, p.max_units, int(ncols), nk, reset);
   } else {
     rbk_merge_kernel<SumT, 1><<<unsigned(ceil_div<int64_t>(nkeys, 8)), 256, 0, stream>>>(
-      sums, counts, partial, offs, uoffs, p.n_windows, p.n_groups, p.max_units, int(ncols), nk, reset);
+      sums, counts, partial, gcnt, uoffs, p.n_groups, p.max_units, int(ncols), nk, reset);
   }
   return cudaGetLastError();
 }
