@@ -77,6 +77,21 @@ B2R_DI bool mbar_try_wait(uint64_t* bar, unsigned parity)
     : "memory");
   return ok != 0;
 }
+// A consumer's place in a ring of `stages` stages - stage index and parity of the round - advanced without a
+// division: tile t sits in stage t % stages in round t / stages, and a division by a run-time stage count costs
+// a warp some thirty instructions per tile (a hundred in 64 bits), as much as the tile's own work where tiles are small.
+struct RingPos {
+  int s;
+  unsigned phase;
+  B2R_DI void advance(int by, int stages)  // by <= stages
+  {
+    s += by;
+    if (s >= stages) {
+      s -= stages;
+      phase ^= 1u;
+    }
+  }
+};
 // Bounded wait. Returns false (and raises the abort flag) when `limit_ns` has passed or another
 // thread has already aborted. The clock is only read once a first batch of polls has failed.
 B2R_DI bool mbar_wait_bounded(uint64_t* bar, unsigned parity, volatile int* abort_flag, unsigned long long limit_ns)
@@ -226,9 +241,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
     }
   } else {
     const int lane = tid & 31;
+    RingPos rp{0, 0u};
     for (int t = 0; t < n_tiles; ++t) {
-      const int s          = t % STAGES;
-      const unsigned phase = (t / STAGES) & 1u;
+      const int s          = rp.s;
+      const unsigned phase = rp.phase;
+      rp.advance(1, STAGES);
       if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) break;
       const int64_t row0 = r_beg + int64_t(t) * tile_rows;
       const int nr       = int((r_end - row0) < tile_rows ? (r_end - row0) : tile_rows);

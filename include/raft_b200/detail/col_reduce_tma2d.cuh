@@ -110,9 +110,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
     }
   } else {
     const int lane = tid & 31;
+    RingPos rp{0, 0u};
     for (int t = 0; t < n_tiles; ++t) {
-      const int s          = t % STAGES;
-      const unsigned phase = (t / STAGES) & 1u;
+      const int s          = rp.s;
+      const unsigned phase = rp.phase;
+      rp.advance(1, STAGES);
       if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) break;
       const int64_t row0 = r_beg + int64_t(t) * kBoxRows;
       const int nr       = int((r_end - row0) < kBoxRows ? (r_end - row0) : kBoxRows);

@@ -4,7 +4,8 @@
 // (linalg/detail/reduce_cols_by_key.cuh:23-68, dispatch :89-138). Two algorithms:
 //  * sorted column tiles for large inputs with up to a few hundred keys: no floating-point atomics,
 //    tiles staged by bulk copies - with a warp walking the sorted columns of its keys (cols_by_key_walk.cuh) for matrices of at least
-//    256 rows and up to 64 keys, with a lane per (row, key) segment (cols_by_key_sorted.cuh) otherwise;
+//    256 rows and up to 64 keys, with a lane per (row, key) segment (cols_by_key_sorted.cuh) otherwise; fp32 with 65 to
+//    255 keys skips the sort and keeps a table cell per (key, row) and warp in shared memory (cols_by_key_table.cuh);
 //  * the kernels of this file otherwise: a CTA owns a tile of RT rows and a contiguous range of
 //    columns, accumulates into a privatised [RT x nkeys] table in shared memory (shared-memory
 //    atomics; lanes of a warp read 128 contiguous bytes of one row per step) and flushes the
@@ -17,6 +18,7 @@
 #include "launch.cuh"
 #include "cols_by_key_sorted.cuh"
 #include "cols_by_key_walk.cuh"
+#include "cols_by_key_table.cuh"
 
 namespace raft_b200 {
 namespace detail {
@@ -93,13 +95,25 @@ __global__ void __launch_bounds__(256) cols_by_key_atomic_kernel(T* __restrict__
   }
 }
 
-// Which sorted-tile form a call takes: 0 none (the kernels of this file), 1 a lane per segment, 2 a warp walking its keys.
+// Which staged form a call takes: 0 none (the kernels of this file), 1 a lane per segment, 2 a warp walking its
+// keys, 3 a table cell per (key, row) in shared memory without sorting (fp32, 65 to 255 keys).
 template <typename T>
-inline int cols_by_key_sorted_form(const T* data, int64_t nrows, int64_t ncols, int64_t nkeys, Cbk32Plan* p32)
+inline int cols_by_key_sorted_form(const T* data, int64_t nrows, int64_t ncols, int64_t nkeys, Cbk32Plan* p32,
+                                   CbkTablePlan* ptab = nullptr)
 {
-  const int algo = tuning().colkey_algo;  // 0: by size, 1: shared-memory atomics, 2: a lane per segment, 3: a warp walking its keys
+  // 0: by size, 1: shared-memory atomics, 2: a lane per segment, 3: a warp walking its keys, 4: table cells
+  const int algo = tuning().colkey_algo;
   if (algo == 1 || !cols_by_key_sorted_supported<T>(nrows, ncols, nkeys)) return 0;
   const bool preferred = cols_by_key_sorted_preferred<T>(nrows, ncols, nkeys);
+  if (algo == 4 || (algo == 0 && preferred && nrows >= 256 && nkeys > tuning().colkey_walk_max_keys &&
+                    nkeys <= tuning().colkey_table_max_keys && tensor_map_dtype<T>::supported &&
+                    encode_tiled_fn() != nullptr)) {
+    const CbkTablePlan p = plan_cols_by_key_table<T>(data, nrows, ncols, nkeys);
+    if (p.ok) {
+      if (ptab != nullptr) *ptab = p;
+      return 3;
+    }
+  }
   if (algo == 3 || (algo == 0 && preferred && nrows >= 256 && nkeys <= tuning().colkey_walk_max_keys)) {
     const Cbk32Plan p = plan_cols_by_key_rows32<T>(data, nrows, ncols, nkeys, tuning().colkey32_ch, tuning().colkey32_rt);
     if (p.ok) {
@@ -118,7 +132,12 @@ inline size_t cols_by_key_scratch_bytes(const T* data, int64_t nrows, int64_t nc
 {
   if (nrows <= 0 || ncols <= 0 || nkeys <= 0) return 0;
   Cbk32Plan p32;
-  const int form = cols_by_key_sorted_form<T>(data, nrows, ncols, nkeys, &p32);
+  CbkTablePlan ptab;
+  const int form = cols_by_key_sorted_form<T>(data, nrows, ncols, nkeys, &p32, &ptab);
+  if (form == 3) {  // should the tensor map fail at the call, the lane-per-segment form runs in the same scratch
+    const size_t other = plan_cols_by_key_sorted<T>(data, nrows, ncols, nkeys).total;
+    return ptab.total > other ? ptab.total : other;
+  }
   if (form == 2) return p32.total;
   if (form == 1) return plan_cols_by_key_sorted<T>(data, nrows, ncols, nkeys).total;
   return 0;
@@ -142,7 +161,14 @@ cudaError_t launch_cols_by_key(T* out,
   // sorted column tiles where they win (large inputs, a few hundred keys at most)
   {
     Cbk32Plan p32;
-    const int form = cols_by_key_sorted_form<T>(data, nrows, ncols, nkeys, &p32);
+    CbkTablePlan ptab;
+    int form = cols_by_key_sorted_form<T>(data, nrows, ncols, nkeys, &p32, &ptab);
+    if (form == 3) {
+      bool unavailable = false;
+      e = launch_cols_by_key_table<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream, ptab, ws, &unavailable);
+      if (!unavailable) return e;
+      form = 1;
+    }
     if (form == 2) return launch_cols_by_key_rows32<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream, p32, ws);
     if (form == 1) return launch_cols_by_key_sorted<T, KeyT>(out, data, keys, nrows, ncols, nkeys, reset, stream, ws);
   }

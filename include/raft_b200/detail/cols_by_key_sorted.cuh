@@ -501,14 +501,16 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __re
       acc[i] = 0.0;
     asm volatile("bar.sync 1, %0;" ::"n"(kCbkConsumers) : "memory");
     long long seq = 0;
+    RingPos rp{0, 0u};
     bool dead     = false;
     for (int64_t rti = rt0; rti < rt1; ++rti) {
       const int64_t r0 = rti * RT;
       const int rt     = int(nrows - r0 < RT ? nrows - r0 : RT);
       for (int c = 0; c < n_ch; ++c, ++seq) {
         if (dead) continue;
-        const int s          = int(seq % STAGES);
-        const unsigned phase = unsigned(seq / STAGES) & 1u;
+        const int s          = rp.s;
+        const unsigned phase = rp.phase;
+        rp.advance(1, STAGES);
         if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) {
           dead = true;
           continue;

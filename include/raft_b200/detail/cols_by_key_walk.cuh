@@ -268,14 +268,16 @@ __global__ void __launch_bounds__(kCbk32Threads, 1) cbk_rows32_kernel(T* __restr
     run[ii] = 0.0;
 
   long long seq = 0;
+  RingPos rp{0, 0u};
   bool dead     = false;
   for (int64_t rti = rt0; rti < rt1; ++rti) {
     const int64_t r0 = rti * RT;
     const int rt     = int(nrows - r0 < RT ? nrows - r0 : RT);
     for (int c = 0; c < n_ch; ++c, ++seq) {
       if (dead) continue;
-      const int s          = int(seq % STAGES);
-      const unsigned phase = unsigned(seq / STAGES) & 1u;
+      const int s          = rp.s;
+      const unsigned phase = rp.phase;
+      rp.advance(1, STAGES);
       if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) {
         dead = true;
         continue;

@@ -121,10 +121,12 @@ struct Tuning {
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
   int key_unit_rows        = 0;     // B2R_KEY_UNIT_ROWS rows of one key a warp sums into one partial row (0: by size, 128..384)
   int key_algo             = 0;     // B2R_KEY_ALGO   0: by size, 1: shared-memory table, 2: sort then stream, 3: one-launch kernel (<= 32768 rows)
-  int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted tiles, a lane per segment, 3: sorted tiles, a warp walking its keys
+  int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted tiles, a lane per segment, 3: sorted tiles, a warp walking its keys, 4: table cells (fp32, up to 255 keys)
   int colkey32_ch          = 0;     // B2R_COLKEY32_CH columns per chunk of the walk form of the keyed column sums (0: the longest that fits)
   int colkey32_rt          = 16;    // B2R_COLKEY32_RT rows per tile of that form: 8, 16 or 32
   int colkey_walk_max_keys = 64;    // B2R_COLKEY_WALK_MAX most keys for which that form is chosen by itself
+  int colkey_table_y       = 0;     // B2R_COLKEY_TABLE_Y column splits of the table form (0: planned)
+  int colkey_table_max_keys = 255;  // B2R_COLKEY_TABLE_MAX_KEYS most keys for the table form of the keyed column sums (fp32)
   int colkey_tma           = 1;     // B2R_COLKEY_TMA 1: TMA-staged ring for the sorted column tiles, 2: off
   int col_tma              = 1;     // B2R_COL_TMA    1: TMA-staged tiles for narrow contiguous column reductions, 2: off
   int col_tma_tile_kb      = 32;    // B2R_COL_TMA_KB tile size of the TMA ring, KiB
@@ -176,6 +178,8 @@ inline Tuning read_tuning_from_env()
   x.colkey32_ch          = env_int("B2R_COLKEY32_CH", x.colkey32_ch);
   x.colkey32_rt          = env_int("B2R_COLKEY32_RT", x.colkey32_rt);
   x.colkey_walk_max_keys = env_int("B2R_COLKEY_WALK_MAX", x.colkey_walk_max_keys);
+  x.colkey_table_y       = env_int("B2R_COLKEY_TABLE_Y", x.colkey_table_y);
+  x.colkey_table_max_keys = env_int("B2R_COLKEY_TABLE_MAX_KEYS", x.colkey_table_max_keys);
   x.colkey_tma           = env_int("B2R_COLKEY_TMA", x.colkey_tma);
   x.col_tma              = env_int("B2R_COL_TMA", x.col_tma);
   x.col_tma_tile_kb      = env_int("B2R_COL_TMA_KB", x.col_tma_tile_kb);

@@ -170,9 +170,11 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T*
   const int n_full = nvec >> lg;                                        // ... that every lane of the group takes
 
   int t = 0;
+  RingPos rp{0, 0u};
   for (; t < n_tiles; ++t) {
-    const int s          = t % STAGES;
-    const unsigned phase = (t / STAGES) & 1u;
+    const int s          = rp.s;
+    const unsigned phase = rp.phase;
+    rp.advance(1, STAGES);
     // a wait that ran out (here, or in the producer) has raised the flag; each consumer reads it BEFORE the
     // barrier and the barrier ORs what they saw, so all of them stay or all of them leave
     mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns);

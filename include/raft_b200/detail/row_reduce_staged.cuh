@@ -122,9 +122,11 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_reduce_staged_kernel(Store
   const int n_rem  = nvec & (G - 1);   // lanes of a group that take one more
 
   int t = 0;
+  RingPos rp{0, 0u};
   for (; t < n_tiles; ++t) {
-    const int s          = t % STAGES;
-    const unsigned phase = (t / STAGES) & 1u;
+    const int s          = rp.s;
+    const unsigned phase = rp.phase;
+    rp.advance(1, STAGES);
     if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) break;
     const int64_t tile_row0 = r_beg + int64_t(t) * tile_rows;
     const int nr            = int((r_end - tile_row0) < tile_rows ? (r_end - tile_row0) : tile_rows);

@@ -134,9 +134,11 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
   const unsigned step_full = unsigned(gpw) * row_bytes;
 
   int t = team;
+  RingPos rp{team, 0u};  // STAGES is a multiple of TEAMS
   for (; t < n_tiles; t += TEAMS) {
-    const int s          = t % STAGES;
-    const unsigned phase = (t / STAGES) & 1u;
+    const int s          = rp.s;
+    const unsigned phase = rp.phase;
+    rp.advance(TEAMS, STAGES);
     if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) break;
     const int64_t tile_row0 = r_beg + int64_t(t) * tile_rows;
     const int nr            = int((r_end - tile_row0) < tile_rows ? (r_end - tile_row0) : tile_rows);
@@ -346,6 +348,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
   const int warp = tid >> 5;
   long long seq  = 0;
   bool dead      = false;
+  RingPos rp{0, 0u};
   for (int64_t row = blockIdx.y; row < n_rows; row += gridDim.y) {
     constexpr int U = 4;
     State st[U];
@@ -354,8 +357,9 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
       init_state<OutT, State, isSum>(st[u], init, direct && tid == 0 && u == 0);
     for (int t = 0; t < tiles_row; ++t, ++seq) {
       if (dead) continue;
-      const int s          = int(seq % STAGES);
-      const unsigned phase = unsigned(seq / STAGES) & 1u;
+      const int s          = rp.s;
+      const unsigned phase = rp.phase;
+      rp.advance(1, STAGES);
       if (!mbar_wait_bounded(&s_full[s], phase, abort_flag, ctl.limit_ns)) {
         dead = true;
         continue;

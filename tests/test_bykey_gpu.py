@@ -79,7 +79,7 @@ def test_rows_by_key_skewed_and_missing_keys(cuda, oracle):
                                                     (3000, 130, 300, np.float64, 1e-9), (32768, 64, 3, np.float32, 1e-5)])
 @pytest.mark.parametrize("weighted", [False, True])
 def test_rows_by_key_sorted_pipeline_on_small_inputs(cuda, oracle, knobs, nobs, cols, nkeys, dt, tol, weighted):
-    """Inputs of up to 32768 rows take the one-launch kernel by default; the six-kernel sorted pipeline must give
+    """Inputs of up to 32768 rows take the one-launch kernel by default; the five-kernel sorted pipeline must give
     the same answers on them."""
     knobs(B2R_KEY_ALGO="2")
     A, hA = device_synth((nobs, cols), dt, 1234, "uniform", -1, 1, cuda)
@@ -214,6 +214,42 @@ def test_cols_by_key_walk_form(cuda, oracle, knobs, rows, cols, nkeys, dt, tol, 
         again = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys)
         assert torch.equal(again, linalg.reduce_cols_by_key(data, keys, nkeys=nkeys))
     assert linalg.last_kernel_status(cuda) == 0
+
+
+# the table form (no sort: a shared-memory cell per key, row and warp; fp32, up to 255 keys), forced, with ragged last
+# boxes and row tiles, columns split over CTAs or not, 8 and 4 consumer warps, a caller's workspace, a key that owns
+# no column, int64 keys, and accumulation into existing sums
+@pytest.mark.parametrize("rows,cols,nkeys", [(1, 1236, 7), (9, 10000, 42), (63, 101012, 127), (1024, 1236, 70),
+                                             (1024, 9996, 255), (4001, 4100, 129), (300, 5004, 1), (20000, 256, 128),
+                                             (7, 228, 4), (2000, 30000, 128), (33, 700000, 200), (257, 228 * 40, 65)])
+@pytest.mark.parametrize("key_dt", [np.int32, np.int64])
+def test_cols_by_key_table_form(cuda, oracle, knobs, rows, cols, nkeys, key_dt):
+    knobs(B2R_COLKEY_ALGO="4")
+    data, hd = device_synth((rows, cols), np.float32, 1234, "uniform", -1, 1, cuda)
+    keys, hk = device_synth((cols,), key_dt, 55, "int", 0, max(1, nkeys - 1), cuda)  # the last key stays empty
+    ws = torch.empty(max(1, linalg.reduce_cols_by_key_workspace_bytes(data, nkeys)), dtype=torch.uint8, device=cuda)
+    out = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys, workspace=ws)
+    exp = oracle.cols_by_key(hd, hk, nkeys)
+    # the cells are fp32: with a handful of keys (forced here; by itself the library takes this form from 65 keys
+    # on) one output is the sum of tens of thousands of fp32 additions and gets the looser bound
+    tol = 1e-5 if nkeys >= 16 else 3e-5
+    oracle.assert_approx(exp, out.cpu().numpy(), tol, "reset")
+    linalg.reduce_cols_by_key(data, keys, out=out, reset_sums=False)
+    oracle.assert_approx(2 * exp, out.cpu().numpy(), 2 * tol, "accumulate")
+    again = linalg.reduce_cols_by_key(data, keys, nkeys=nkeys)
+    assert torch.equal(again, linalg.reduce_cols_by_key(data, keys, nkeys=nkeys))  # fixed order of all additions
+    assert linalg.last_kernel_status(cuda) == 0
+
+
+def test_cols_by_key_table_form_by_itself_and_against_the_other_forms(cuda, oracle, knobs):
+    data, hd = device_synth((1000, 60000), np.float32, 8, "normal", 0, 1, cuda)
+    keys, hk = device_synth((60000,), np.int32, 9, "int", 0, 100, cuda)
+    exp = oracle.cols_by_key(hd, hk, 100)
+    out = linalg.reduce_cols_by_key(data, keys, nkeys=100)  # 100 keys, 240 MB: the table form by the library's choice
+    oracle.assert_approx(exp, out.cpu().numpy(), 1e-5, "auto")
+    knobs(B2R_COLKEY_ALGO="2")
+    seg = linalg.reduce_cols_by_key(data, keys, nkeys=100)
+    oracle.assert_approx(seg.cpu().numpy().astype(np.float64), out.cpu().numpy(), 1e-5, "against a lane per segment")
 
 
 def test_cols_by_key_single_kernel_path(cuda, oracle, knobs):

@@ -102,6 +102,15 @@ def test_keyed_column_sums_walk_ring(cuda, knobs):
                             lambda o: torch.all(o == 2048.0).item() or pytest.fail("keyed column sums wrong"))
 
 
+def test_keyed_column_sums_table_ring(cuda, knobs):
+    t = torch.ones((512, 32768), dtype=torch.float32, device=cuda)
+    keys = (torch.arange(32768, device=cuda, dtype=torch.int32) % 100).contiguous()
+    want = torch.bincount(keys.long(), minlength=100).to(torch.float32)
+    _expect_timeout_then_ok(cuda, knobs, {"B2R_COLKEY_ALGO": "4"}, lambda: linalg.reduce_cols_by_key(t, keys, nkeys=100),
+                            lambda o: torch.isnan(o).any().item() or pytest.fail("unfinished sums not NaN"),
+                            lambda o: torch.all(o == want[None, :]).item() or pytest.fail("keyed column sums wrong"))
+
+
 def test_wait_limit_setter_and_status_string(cuda):
     lib = L.load()
     assert lib.b2r_set_wait_limit_ms(250) == L.OK
