@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(TPB, 4) col_partial_kernel(OutT* __restrict__ 
                                                          int TX,
                                                          int64_t rows_per_cta)
 {
+  grid_dep_sync();
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -131,6 +132,7 @@ __global__ void __launch_bounds__(TPB) col_finalize_kernel(OutT* __restrict__ ou
                                                           FinalOp final_op,
                                                           const int* __restrict__ cta_status = nullptr)
 {
+  grid_dep_sync();
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
   const int lane       = threadIdx.x & 31;

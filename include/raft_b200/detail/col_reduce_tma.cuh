@@ -195,10 +195,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
       mbar_init(&s_empty[s], kTmaConsumers / 32);
     }
     s_abort = 0;
-    if (cta_status != nullptr) cta_status[blockIdx.x] = 0;  // 1 if this CTA gave up on a wait
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  grid_dep_sync();  // the set-up above touches shared memory only
+  // 1 if this CTA gave up on a wait (set by the same thread)
+  if (tid == kTmaConsumers && cta_status != nullptr) cta_status[blockIdx.x] = 0;
   volatile int* abort_flag = &s_abort;
 
   State st[VEC];

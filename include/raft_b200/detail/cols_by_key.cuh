@@ -114,7 +114,10 @@ inline int cols_by_key_sorted_form(const T* data, int64_t nrows, int64_t ncols, 
       return 3;
     }
   }
-  if (algo == 3 || (algo == 0 && preferred && nrows >= 256 && nkeys <= tuning().colkey_walk_max_keys)) {
+  // (types the table form does not take keep the walk up to 64 keys, where it still beats a lane per segment)
+  const int walk_max = std::is_same<T, float>::value ? tuning().colkey_walk_max_keys
+                                                      : (tuning().colkey_walk_max_keys > 64 ? tuning().colkey_walk_max_keys : 64);
+  if (algo == 3 || (algo == 0 && preferred && nrows >= 256 && nkeys <= walk_max)) {
     const Cbk32Plan p = plan_cols_by_key_rows32<T>(data, nrows, ncols, nkeys, tuning().colkey32_ch, tuning().colkey32_rt);
     if (p.ok) {
       if (p32 != nullptr) *p32 = p;

@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(kCbkTpb) cbk_sort_kernel(const KeyT* __restric
                                                           unsigned short* __restrict__ perm16,
                                                           unsigned short* __restrict__ offs16)
 {
+  grid_dep_sync();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int* s_cnt = reinterpret_cast<int*>(smem_raw);  // [nkeys] counts, then scatter cursors
   __shared__ int s_warp[kCbkTpb / 32];
@@ -317,6 +318,7 @@ __global__ void __launch_bounds__(256) cbk_merge_kernel(T* __restrict__ out,
                                                        int y_split,
                                                        bool reset)
 {
+  grid_dep_sync();
   const int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
   if (i >= n_cells) return;
   double s = reset ? 0.0 : double(out[i]);
@@ -426,6 +428,7 @@ __global__ void __launch_bounds__(kCbkTmaThreads, 2) cbk_tile_tma_kernel(T* __re
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  grid_dep_sync();  // the set-up above touches shared memory only
   volatile int* abort_flag = &s_abort;
 
   if (producer) {
@@ -735,8 +738,8 @@ cudaError_t launch_cols_by_key_sorted(T* out,
   const int nk           = int(nkeys);
   cudaError_t e;
 
-  cbk_sort_kernel<KeyT><<<unsigned(p.n_chunks), kCbkTpb, size_t(nk) * sizeof(int), stream>>>(
-    keys, ncols, nk, p.CH, p.offs_stride, perm16, offs16);
+  (void)launch_dep(cbk_sort_kernel<KeyT>, dim3(unsigned(p.n_chunks)), dim3(kCbkTpb), size_t(nk) * sizeof(int), stream,
+                   keys, ncols, nk, p.CH, p.offs_stride, perm16, offs16);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
@@ -747,10 +750,9 @@ cudaError_t launch_cols_by_key_sorted(T* out,
     e = ensure_dynamic_smem(kern, size_t(p.smem));
     if (e != cudaSuccess) return e;
     const dim3 grid{unsigned(ceil_div<int64_t>(p.n_row_tiles, p.row_tiles_per_cta)), unsigned(p.y_split), 1u};
-    kern<<<grid, kCbkTmaThreads, p.smem, stream>>>(out, partial, data, perm16, offs16, nrows, ncols, nk, p.RT, p.CH,
-                                                   p.offs_stride, p.n_chunks, p.chunks_per_cta, p.n_row_tiles,
-                                                   p.row_tiles_per_cta, p.stages, reset, stage, p.acc_bytes,
-                                                   ring_ctl(ws.status));
+    (void)launch_dep(kern, dim3(grid), dim3(kCbkTmaThreads), p.smem, stream, out, partial, data, perm16, offs16,
+                     nrows, ncols, nk, p.RT, p.CH, p.offs_stride, p.n_chunks, p.chunks_per_cta, p.n_row_tiles,
+                     p.row_tiles_per_cta, p.stages, reset, stage, p.acc_bytes, ring_ctl(ws.status));
   } else {
   const CbkSmem<T> lay = cbk_smem<T>(p.RT, p.CH, nk);
   const dim3 grid{unsigned(p.n_row_tiles), unsigned(p.y_split), 1u};
@@ -776,8 +778,8 @@ cudaError_t launch_cols_by_key_sorted(T* out,
   e = cudaGetLastError();
   if (e != cudaSuccess || p.y_split == 1) return e;
   const int64_t cells = nrows * nkeys;
-  cbk_merge_kernel<T><<<unsigned(ceil_div<int64_t>(cells, 256)), 256, 0, stream>>>(out, partial, cells, p.y_split,
-                                                                                  reset);
+  (void)launch_dep(cbk_merge_kernel<T>, dim3(unsigned(ceil_div<int64_t>(cells, 256))), dim3(256), 0, stream, out,
+                   partial, cells, p.y_split, reset);
   return cudaGetLastError();
 }
 

@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(256) cbk_keys8_kernel(unsigned char* __restric
                                                        int nkeys,
                                                        int n_chunks)
 {
+  grid_dep_sync();
   const int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
   if (i >= int64_t(n_chunks) * kCbkTableKeyB) return;
   const int ch     = int(i / kCbkTableKeyB);
@@ -257,6 +258,7 @@ __global__ void __launch_bounds__(W * 32 + 32, 1) cbk_table_kernel(T* __restrict
   for (uint32_t i = uint32_t(tid) * 16u; i < uint32_t(W) * uint32_t(P.table_bytes); i += blockDim.x * 16u)
     *reinterpret_cast<float4*>(smem_tma + i) = make_float4(0.f, 0.f, 0.f, 0.f);
   __syncthreads();
+  grid_dep_sync();  // the set-up above touches shared memory only
   volatile int* abort_flag = &s_abort;
 
   if (producer) {
@@ -442,18 +444,21 @@ cudaError_t launch_cols_by_key_table(T* out,
     double* partial      = reinterpret_cast<double*>(base + p.off_part_g);
     const int nk         = int(nkeys);
     const int64_t nb     = int64_t(p.n_chunks) * kCbkTableKeyB;
-    cbk_keys8_kernel<KeyT><<<unsigned(ceil_div<int64_t>(nb, 256)), 256, 0, stream>>>(keys8, keys, ncols, nk, p.n_chunks);
+    (void)launch_dep(cbk_keys8_kernel<KeyT>, dim3(unsigned(ceil_div<int64_t>(nb, 256))), dim3(256), 0, stream, keys8,
+                     keys, ncols, nk, p.n_chunks);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     auto kern = p.warps == 8 ? cbk_table_kernel<T, 8> : cbk_table_kernel<T, 4>;
     e         = ensure_dynamic_smem(kern, p.smem);
     if (e != cudaSuccess) return e;
     const dim3 grid{unsigned(ceil_div<int64_t>(p.n_row_tiles, p.row_tiles_per_cta)), unsigned(p.y_split), 1u};
-    kern<<<grid, p.warps * 32 + 32, p.smem, stream>>>(out, partial, tmap, keys8, nrows, nk, reset, p, ring_ctl(ws.status));
+    (void)launch_dep(kern, dim3(grid), dim3(p.warps * 32 + 32), p.smem, stream, out, partial, tmap, keys8, nrows, nk,
+                     reset, p, ring_ctl(ws.status));
     e = cudaGetLastError();
     if (e != cudaSuccess || p.y_split == 1) return e;
     const int64_t cells = nrows * nkeys;
-    cbk_merge_kernel<T><<<unsigned(ceil_div<int64_t>(cells, 256)), 256, 0, stream>>>(out, partial, cells, p.y_split, reset);
+    (void)launch_dep(cbk_merge_kernel<T>, dim3(unsigned(ceil_div<int64_t>(cells, 256))), dim3(256), 0, stream, out,
+                     partial, cells, p.y_split, reset);
     return cudaGetLastError();
   }
 }

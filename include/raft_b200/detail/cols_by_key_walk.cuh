@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(kCbk32Threads, 1) cbk_rows32_kernel(T* __restr
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  grid_dep_sync();  // the set-up above touches shared memory only
   volatile int* abort_flag = &s_abort;
 
   if (producer) {
@@ -377,8 +378,8 @@ cudaError_t launch_cols_by_key_rows32(T* out,
   unsigned short* offs16 = reinterpret_cast<unsigned short*>(base + p.off_offs_g);
   double* partial        = reinterpret_cast<double*>(base + p.off_part_g);
   const int nk           = int(nkeys);
-  cbk_sort_kernel<KeyT><<<unsigned(p.n_chunks), kCbkTpb, size_t(nk) * sizeof(int), stream>>>(
-    keys, ncols, nk, p.CH, p.offs_stride, perm16, offs16);
+  (void)launch_dep(cbk_sort_kernel<KeyT>, dim3(unsigned(p.n_chunks)), dim3(kCbkTpb), size_t(nk) * sizeof(int), stream,
+                   keys, ncols, nk, p.CH, p.offs_stride, perm16, offs16);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const dim3 grid{unsigned(ceil_div<int64_t>(p.n_row_tiles, p.row_tiles_per_cta)), unsigned(p.y_split), 1u};
@@ -387,7 +388,8 @@ cudaError_t launch_cols_by_key_rows32(T* out,
     auto kern = cbk_rows32_kernel<T, IPW_>;                                                                        \
     e         = ensure_dynamic_smem(kern, p.smem);                                                                 \
     if (e != cudaSuccess) return e;                                                                                \
-    kern<<<grid, kCbk32Threads, p.smem, stream>>>(out, partial, data, perm16, offs16, nrows, ncols, nk, reset, p, \
+    (void)launch_dep(kern, dim3(grid), dim3(kCbk32Threads), p.smem, stream,                                        \
+                     out, partial, data, perm16, offs16, nrows, ncols, nk, reset, p,                               \
                                                  ring_ctl(ws.status));                                             \
   } while (0)
   if (p.items_per_warp <= 1) {
@@ -405,7 +407,8 @@ cudaError_t launch_cols_by_key_rows32(T* out,
   e = cudaGetLastError();
   if (e != cudaSuccess || p.y_split == 1) return e;
   const int64_t cells = nrows * nkeys;
-  cbk_merge_kernel<T><<<unsigned(ceil_div<int64_t>(cells, 256)), 256, 0, stream>>>(out, partial, cells, p.y_split, reset);
+  (void)launch_dep(cbk_merge_kernel<T>, dim3(unsigned(ceil_div<int64_t>(cells, 256))), dim3(256), 0, stream, out,
+                   partial, cells, p.y_split, reset);
   return cudaGetLastError();
 }
 

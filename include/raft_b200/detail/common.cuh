@@ -62,6 +62,16 @@ struct vec16 {
   static constexpr int value = (sizeof(T) <= 16 && 16 % sizeof(T) == 0) ? int(16 / sizeof(T)) : 1;
 };
 
+// Programmatic dependent launch. A kernel launched with launch_dep() (launch.cuh) may be scheduled while the
+// previous kernel of the stream is still draining: it announces first that ITS successor may be scheduled
+// likewise, then waits until the predecessor has completed and its writes are visible. Everything before the
+// wait must stay off global memory. Both instructions do nothing in a kernel launched the ordinary way.
+B2R_DI void grid_dep_sync()
+{
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // Streaming load: the matrix is read exactly once, so it bypasses L1 allocation
 // (ld.global.nc.L1::no_allocate). 32-byte vectors use the 256-bit load of sm_100, which can
 // also mark the line evict-first in L2. Falls back to plain loads for odd sizes.

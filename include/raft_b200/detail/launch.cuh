@@ -124,7 +124,7 @@ struct Tuning {
   int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted tiles, a lane per segment, 3: sorted tiles, a warp walking its keys, 4: table cells (fp32, up to 255 keys)
   int colkey32_ch          = 0;     // B2R_COLKEY32_CH columns per chunk of the walk form of the keyed column sums (0: the longest that fits)
   int colkey32_rt          = 16;    // B2R_COLKEY32_RT rows per tile of that form: 8, 16 or 32
-  int colkey_walk_max_keys = 64;    // B2R_COLKEY_WALK_MAX most keys for which that form is chosen by itself
+  int colkey_walk_max_keys = 40;    // B2R_COLKEY_WALK_MAX most keys for which that form is chosen by itself (fp32: the table form takes over)
   int colkey_table_y       = 0;     // B2R_COLKEY_TABLE_Y column splits of the table form (0: planned)
   int colkey_table_max_keys = 255;  // B2R_COLKEY_TABLE_MAX_KEYS most keys for the table form of the keyed column sums (fp32)
   int colkey_tma           = 1;     // B2R_COLKEY_TMA 1: TMA-staged ring for the sorted column tiles, 2: off
@@ -150,6 +150,7 @@ struct Tuning {
   int row_staged_ring_kb   = 100;   // B2R_ROW_STAGED_RING_KB shared memory of one CTA's ring, KiB (100: two CTAs per SM)
   int row_split_ring       = 1;     // B2R_ROW_SPLIT_RING 1: ring of bulk copies for a handful of very long rows, 2: off
   int row_split_ring_min_mb = 64;   // B2R_ROW_SPLIT_RING_MB shortest row (MiB) that takes it
+  int dep_launch           = 1;     // B2R_DEP_LAUNCH 1: kernels that begin with grid_dep_sync() are launched with programmatic stream serialization, 2: ordinary launches
   int wait_limit_ms        = 1000;  // B2R_WAIT_LIMIT_MS bound of every mbarrier wait inside the ring kernels, milliseconds
   int test_skip_tile       = 0;     // B2R_TEST_SKIP_TILE test hook: the producer of the first CTA never requests tile (value - 1)
 };
@@ -208,6 +209,7 @@ inline Tuning read_tuning_from_env()
   if (x.row_staged_ring_kb > 200) x.row_staged_ring_kb = 200;
   x.row_split_ring       = env_int("B2R_ROW_SPLIT_RING", x.row_split_ring);
   x.row_split_ring_min_mb = env_int("B2R_ROW_SPLIT_RING_MB", x.row_split_ring_min_mb);
+  x.dep_launch           = env_int("B2R_DEP_LAUNCH", x.dep_launch);
   x.wait_limit_ms        = env_int("B2R_WAIT_LIMIT_MS", x.wait_limit_ms);
   x.test_skip_tile       = env_int("B2R_TEST_SKIP_TILE", x.test_skip_tile);
   return x;
@@ -283,6 +285,26 @@ template <typename Kernel>
 inline cudaError_t ensure_dynamic_smem(Kernel kern, size_t bytes)
 {
   return ensure_dynamic_smem(reinterpret_cast<const void*>(kern), bytes);
+}
+
+// Launch of a kernel that begins with grid_dep_sync(): with programmatic stream serialization its CTAs may be
+// scheduled while the previous kernel of the stream drains (measured: 2-4 us per kernel boundary). ONLY for
+// kernels that call grid_dep_sync() before their first access to global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args)
+{
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = grid;
+  cfg.blockDim           = block;
+  cfg.dynamicSmemBytes   = smem;
+  cfg.stream             = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs                                        = at;
+  cfg.numAttrs                                     = tuning().dep_launch == 1 ? 1u : 0u;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
 }
 
 // Resident CTAs per SM of a kernel: the reductions launch one or two resident waves of
@@ -500,31 +522,31 @@ cudaError_t launch_row_reduce(StoreT* out,
         cudaError_t ea    = ensure_dynamic_smem(kern, smem);
         if (ea != cudaSuccess) return ea;
         const dim3 rgrid{unsigned(segs), unsigned(n_rows), 1u};
-        kern<<<rgrid, kTmaThreads, smem, stream>>>(out, partial, data, n_rows, row_len, ld, init, inplace, main_op,
-                                                  reduce_op, final_op, sv, tile_vecs, stages, ring_ctl(ws.status));
+        (void)launch_dep(kern, dim3(rgrid), dim3(kTmaThreads), smem, stream, out, partial, data, n_rows, row_len, ld,
+                         init, inplace, main_op, reduce_op, final_op, sv, tile_vecs, stages, ring_ctl(ws.status));
         ea = cudaGetLastError();
         if (ea != cudaSuccess || segs == 1) return ea;
-        row_finalize_kernel<OutT, ReduceOp, FinalOp, TPB, StoreT>
-          <<<unsigned(ceil_div<int64_t>(n_rows, TPB / 32)), TPB, 0, stream>>>(
-            out, partial, n_rows, int(segs), init, inplace, reduce_op, final_op);
+        (void)launch_dep(row_finalize_kernel<OutT, ReduceOp, FinalOp, TPB, StoreT>,
+                         dim3(unsigned(ceil_div<int64_t>(n_rows, TPB / 32))), dim3(TPB), 0, stream, out, partial,
+                         n_rows, int(segs), init, inplace, reduce_op, final_op);
         return cudaGetLastError();
       }
     }
     const dim3 grid{unsigned(n_seg), unsigned(n_rows < 65535 ? n_rows : 65535), 1u};
     if (vec_split) {
-      row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, 4, TPB, StoreT>
-        <<<grid, TPB, 0, stream>>>(
-          out, partial, data, n_rows, row_len, ld, init, inplace, main_op, reduce_op, final_op, seg_vecs);
+      (void)launch_dep(row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, 4, TPB, StoreT>, dim3(grid),
+                       dim3(TPB), 0, stream, out, partial, data, n_rows, row_len, ld, init, inplace, main_op,
+                       reduce_op, final_op, seg_vecs);
     } else {
-      row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, 1, 4, TPB, StoreT>
-        <<<grid, TPB, 0, stream>>>(
-          out, partial, data, n_rows, row_len, ld, init, inplace, main_op, reduce_op, final_op, seg_vecs);
+      (void)launch_dep(row_split_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, 1, 4, TPB, StoreT>, dim3(grid),
+                       dim3(TPB), 0, stream, out, partial, data, n_rows, row_len, ld, init, inplace, main_op,
+                       reduce_op, final_op, seg_vecs);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || n_seg == 1) return e;
-    row_finalize_kernel<OutT, ReduceOp, FinalOp, TPB, StoreT>
-      <<<unsigned(ceil_div<int64_t>(n_rows, TPB / 32)), TPB, 0, stream>>>(
-        out, partial, n_rows, n_seg, init, inplace, reduce_op, final_op);
+    (void)launch_dep(row_finalize_kernel<OutT, ReduceOp, FinalOp, TPB, StoreT>,
+                     dim3(unsigned(ceil_div<int64_t>(n_rows, TPB / 32))), dim3(TPB), 0, stream, out, partial, n_rows,
+                     n_seg, init, inplace, reduce_op, final_op);
     return cudaGetLastError();
   }
 
@@ -579,7 +601,7 @@ cudaError_t launch_row_reduce(StoreT* out,
     auto kern      = row_reduce_ring_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, U_, CPL_, kRingTeams, StoreT>; \
     cudaError_t ea = ensure_dynamic_smem(kern, smem);                                                          \
     if (ea != cudaSuccess) return ea;                                                                          \
-    kern<<<unsigned(ctas), kRingTeams * kTmaConsumers + 32, smem, stream>>>(                                   \
+    (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(kRingTeams * kTmaConsumers + 32), smem, stream,          \
       out, data, n_rows, int(row_len), init, inplace, main_op, reduce_op, final_op, G, int(tile_rows), rpc,    \
       stages, ring_ctl(ws.status));                                                                            \
   } while (0)
@@ -624,9 +646,9 @@ cudaError_t launch_row_reduce(StoreT* out,
     auto kern      = row_reduce_staged_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, StoreT>;     \
     cudaError_t ea = ensure_dynamic_smem(kern, smem);                                                        \
     if (ea != cudaSuccess) return ea;                                                                        \
-    kern<<<unsigned(ctas), kTmaThreads, smem, stream>>>(out, data, n_main, int(row_len), init, inplace,      \
-                                                       main_op, reduce_op, final_op, Gs, rot, int(tile_rows), \
-                                                       rpc, stages, ring_ctl(ws.status));                    \
+    (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(kTmaThreads), smem, stream, out, data, n_main,         \
+                     int(row_len), init, inplace, main_op, reduce_op, final_op, Gs, rot, int(tile_rows),     \
+                     rpc, stages, ring_ctl(ws.status));                                                      \
   } while (0)
         if (vec_ok) {
           B2R_LAUNCH_STAGED(V16);
@@ -685,7 +707,7 @@ cudaError_t launch_row_reduce(StoreT* out,
       }                                                                                          \
     }                                                                                            \
     ctas        = ceil_div<int64_t>(n_b, bpc);                                                   \
-    kern<<<unsigned(ctas), TPB, 0, stream>>>(                                                    \
+    (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(TPB), 0, stream,                           \
       out, data, n_rows, rl, ld, init, inplace, main_op, reduce_op, final_op,                    \
       shifted ? G_shifted : G,                                                                   \
       bpc, shifted);                                                                             \
@@ -915,14 +937,14 @@ cudaError_t launch_col_reduce(OutT* out,
       auto kern       = col_partial_tma_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16>;
       cudaError_t ea  = ensure_dynamic_smem(kern, size_t(p.smem));
       if (ea != cudaSuccess) return ea;
-      kern<<<p.grid_x, kTmaThreads, p.smem, stream>>>(out, partial, data, n_rows, int(n_cols), init, inplace, main_op,
-                                                     reduce_op, final_op, p.TX, p.tile_rows, p.rows_per_cta,
-                                                     p.stages, cta_status, ring_ctl(ws.status));
+      (void)launch_dep(kern, dim3(p.grid_x), dim3(kTmaThreads), p.smem, stream, out, partial, data, n_rows,
+                       int(n_cols), init, inplace, main_op, reduce_op, final_op, p.TX, p.tile_rows, p.rows_per_cta,
+                       p.stages, cta_status, ring_ctl(ws.status));
       ea = cudaGetLastError();
       if (ea != cudaSuccess) return ea;
       const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));
-      col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin, TPB, 0, stream>>>(
-        out, partial, int(p.grid_x), n_cols, init, inplace, reduce_op, final_op, cta_status);
+      (void)launch_dep(col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB>, dim3(fin), dim3(TPB), 0, stream, out,
+                       partial, int(p.grid_x), n_cols, init, inplace, reduce_op, final_op, cta_status);
       return cudaGetLastError();
     }
   }
@@ -938,14 +960,14 @@ cudaError_t launch_col_reduce(OutT* out,
         ea        = ensure_dynamic_smem(kern, size_t(p.smem));
         if (ea != cudaSuccess) return ea;
         const dim3 grid2(p.grid_x, p.grid_y);
-        kern<<<grid2, kTmaThreads, p.smem, stream>>>(out, partial, tmap, n_rows, n_cols, init, inplace, main_op,
-                                                    reduce_op, final_op, p.rows_per_cta, p.stages, cta_status,
-                                                    ring_ctl(ws.status));
+        (void)launch_dep(kern, dim3(grid2), dim3(kTmaThreads), p.smem, stream, out, partial, tmap, n_rows, n_cols,
+                         init, inplace, main_op, reduce_op, final_op, p.rows_per_cta, p.stages, cta_status,
+                         ring_ctl(ws.status));
         ea = cudaGetLastError();
         if (ea != cudaSuccess) return ea;
         const unsigned fin = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));
-        col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin, TPB, 0, stream>>>(
-          out, partial, int(p.grid_y), n_cols, init, inplace, reduce_op, final_op, cta_status);
+        (void)launch_dep(col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB>, dim3(fin), dim3(TPB), 0, stream, out,
+                         partial, int(p.grid_y), n_cols, init, inplace, reduce_op, final_op, cta_status);
         return cudaGetLastError();
       }
       // no tensor map (driver entry point missing): the register-staged plan, whose partial rows
@@ -959,19 +981,19 @@ cudaError_t launch_col_reduce(OutT* out,
   const dim3 grid(p.grid_x, p.grid_y);
 
   if (p.vec > 1) {
-    col_partial_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, U, TPB>
-      <<<grid, TPB, p.smem, stream>>>(out, partial, data, n_rows, n_cols, ld, init, inplace,
-                                      main_op, reduce_op, final_op, p.TX, p.rows_per_cta);
+    (void)launch_dep(col_partial_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, V16, U, TPB>, dim3(grid),
+                     dim3(TPB), p.smem, stream, out, partial, data, n_rows, n_cols, ld, init, inplace, main_op,
+                     reduce_op, final_op, p.TX, p.rows_per_cta);
   } else {
-    col_partial_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, 1, U, TPB>
-      <<<grid, TPB, p.smem, stream>>>(out, partial, data, n_rows, n_cols, ld, init, inplace,
-                                      main_op, reduce_op, final_op, p.TX, p.rows_per_cta);
+    (void)launch_dep(col_partial_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, 1, U, TPB>, dim3(grid), dim3(TPB),
+                     p.smem, stream, out, partial, data, n_rows, n_cols, ld, init, inplace, main_op, reduce_op,
+                     final_op, p.TX, p.rows_per_cta);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || p.grid_y == 1) return e;
   const unsigned fin_ctas = unsigned(ceil_div<int64_t>(n_cols, TPB / 32));
-  col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB><<<fin_ctas, TPB, 0, stream>>>(
-    out, partial, int(p.grid_y), n_cols, init, inplace, reduce_op, final_op);
+  (void)launch_dep(col_finalize_kernel<OutT, ReduceOp, FinalOp, TPB>, dim3(fin_ctas), dim3(TPB), 0, stream, out,
+                   partial, int(p.grid_y), n_cols, init, inplace, reduce_op, final_op, static_cast<const int*>(nullptr));
   return cudaGetLastError();
 }
 

@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(256) row_normalize_kernel(T* out,
                                                            FinalOp final_op,
                                                            int G)
 {
+  grid_dep_sync();
   using State = typename state_for<T, ReduceOp>::type;
   const int lane = threadIdx.x & 31;
   const int lg   = 31 - __clz(G);
@@ -114,6 +115,7 @@ __global__ void __launch_bounds__(256) row_normalize_cta_kernel(T* out,
                                                                ReduceOp reduce_op,
                                                                FinalOp final_op)
 {
+  grid_dep_sync();
   using State = typename state_for<T, ReduceOp>::type;
   __shared__ State s_state[2][8];  // double-buffered: one barrier per row
   const int tid  = threadIdx.x;
@@ -181,6 +183,7 @@ __global__ void __launch_bounds__(256) row_normalize_long_kernel(T* out,
                                                                 ReduceOp reduce_op,
                                                                 FinalOp final_op)
 {
+  grid_dep_sync();
   using State     = typename state_for<T, ReduceOp>::type;
   using Vec       = VecOf<T, VEC>;
   constexpr int Q = 4;  // loads in flight per thread
@@ -289,7 +292,8 @@ cudaError_t launch_row_normalize(T* out,
     auto kern      = row_normalize_staged_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_>;                   \
     cudaError_t ea = ensure_dynamic_smem(kern, smem);                                                         \
     if (ea != cudaSuccess) return ea;                                                                         \
-    kern<<<unsigned(sp.ctas), kTmaThreads, smem, stream>>>(out, in, sp.n_main, int(n_cols), init, eps, main_op, \
+    (void)launch_dep(kern, dim3(unsigned(sp.ctas)), dim3(kTmaThreads), smem, stream,                                  \
+                     out, in, sp.n_main, int(n_cols), init, eps, main_op,                                             \
                                                           reduce_op, final_op, sp.G, sp.rot, int(sp.tile_rows), \
                                                           sp.rows_per_cta, sp.stages, ring_ctl(status));      \
   } while (0)
@@ -320,7 +324,8 @@ cudaError_t launch_row_normalize(T* out,
     int64_t ctas               = ceil_div<int64_t>(n_rows, rows_per_cta);                                 \
     const int64_t cap          = int64_t(sms) * occ * 2;                                                  \
     if (ctas > cap) ctas = cap;                                                                           \
-    kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,      \
+    (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(256), 0, stream,                                                \
+                     out, in, n_rows, n_cols, init, eps, main_op, reduce_op,                                          \
                                              final_op, G);                                                \
   } while (0)
 #define B2R_NORMALIZE_CTA(VEC_, CPT_)                                                                     \
@@ -329,7 +334,8 @@ cudaError_t launch_row_normalize(T* out,
     static int occ = resident_ctas(kern, 256, 0);                                                         \
     int64_t ctas   = n_rows;                                                                              \
     if (ctas > int64_t(sms) * occ * 2) ctas = int64_t(sms) * occ * 2;                                     \
-    kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,      \
+    (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(256), 0, stream,                                                \
+                     out, in, n_rows, n_cols, init, eps, main_op, reduce_op,                                          \
                                              final_op);                                                   \
   } while (0)
 #define B2R_NORMALIZE_ANY(VEC_)                                                                           \
@@ -339,7 +345,8 @@ cudaError_t launch_row_normalize(T* out,
       static int occ = resident_ctas(kern, 256, 0);                                                       \
       int64_t ctas   = n_rows;                                                                            \
       if (ctas > int64_t(sms) * occ) ctas = int64_t(sms) * occ;                                           \
-      kern<<<unsigned(ctas), 256, 0, stream>>>(out, in, n_rows, n_cols, init, eps, main_op, reduce_op,    \
+      (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(256), 0, stream,                                              \
+                       out, in, n_rows, n_cols, init, eps, main_op, reduce_op,                                        \
                                                final_op);                                                 \
     } else if (nvec > 2048) {                                                                             \
       B2R_NORMALIZE_CTA(VEC_, 16);                                                                        \

@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) row_normalize_staged_kernel(T*
   for (int w = tid; w < STAGES * flag_words; w += kTmaThreads)
     flags_base[w] = 0u;
   __syncthreads();
+  grid_dep_sync();  // the set-up above touches shared memory only
   volatile int* abort_flag = &s_abort;
   volatile int* skip_flag  = s_skip;
 

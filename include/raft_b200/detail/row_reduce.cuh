@@ -155,6 +155,7 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
 {
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
+  grid_dep_sync();
 
   const int lane  = threadIdx.x & 31;
   const int lg    = 31 - __clz(G);    // G is a power of two
@@ -384,6 +385,7 @@ __global__ void __launch_bounds__(TPB) row_split_kernel(StoreT* __restrict__ out
                                                        FinalOp final_op,
                                                        int64_t seg_vecs)
 {
+  grid_dep_sync();
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
   __shared__ State s_warp[TPB / 32];
@@ -459,6 +461,7 @@ __global__ void __launch_bounds__(TPB) row_finalize_kernel(StoreT* __restrict__ 
                                                           ReduceOp reduce_op,
                                                           FinalOp final_op)
 {
+  grid_dep_sync();
   using State          = typename state_for<OutT, ReduceOp>::type;
   constexpr bool isSum = is_sum_op<ReduceOp>::value && std::is_floating_point<OutT>::value;
   const int lane       = threadIdx.x & 31;

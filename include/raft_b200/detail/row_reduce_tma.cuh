@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(TEAMS * kTmaConsumers + 32, 1) row_reduce_ring
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  grid_dep_sync();  // the set-up above touches shared memory only
   volatile int* abort_flag = &s_abort;
 
   if (producer) {
@@ -305,6 +306,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  grid_dep_sync();  // the set-up above touches shared memory only
   volatile int* abort_flag = &s_abort;
 
   if (producer) {

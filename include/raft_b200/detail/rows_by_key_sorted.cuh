@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(kSortTpb) rbk_sort_kernel(const KeyT* __restri
                                                            int* __restrict__ offs,
                                                            int* __restrict__ unit_counter)
 {
+  grid_dep_sync();
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     unit_counter[0] = 0;  // the stream kernel's work queue
     unit_counter[1] = 0;  // length of the fold list
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(TPB) rbk_units_kernel(const int* __restrict__ 
                                                        int* __restrict__ fold_list,
                                                        int* __restrict__ fold_count)
 {
+  grid_dep_sync();
   static_assert(TPB / 32 <= 32, "one warp scans the warp totals");
   __shared__ int s_warp[TPB / 32];
   __shared__ int s_total;
@@ -295,6 +297,7 @@ __global__ void __launch_bounds__(256, 3) rbk_stream_kernel(typename sum_state<S
                                                         const int* __restrict__ ulen,
                                                         int* __restrict__ unit_counter)
 {
+  grid_dep_sync();
   using State     = typename sum_state<SumT>::type;
   using CarryT    = typename State::carry_t;
   constexpr int Q = 8;  // row loads in flight per lane
@@ -435,6 +438,7 @@ __global__ void __launch_bounds__(256) rbk_fold_kernel(typename sum_state<SumT>:
                                                       int ncols,
                                                       int nkeys)
 {
+  grid_dep_sync();
   using State  = typename sum_state<SumT>::type;
   using CarryT = typename State::carry_t;
   constexpr int R = 8;
@@ -498,6 +502,7 @@ __global__ void __launch_bounds__(256) rbk_merge_kernel(SumT* __restrict__ sums,
                                                        int nkeys,
                                                        bool reset)
 {
+  grid_dep_sync();
   using State  = typename sum_state<SumT>::type;
   using CarryT = typename State::carry_t;
   static_assert(WPK == 1 || WPK == 8, "one warp or one CTA per key");
@@ -715,16 +720,13 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
     e = ensure_dynamic_smem(sort_kern, size_t(sort_smem));
     if (e != cudaSuccess) return e;
   }
-  sort_kern<<<unsigned(p.n_windows), kSortTpb, sort_smem, stream>>>(keys, nrows, nk, p.window_rows, perm, offs,
-                                                                    counter);
-  e = cudaGetLastError();
+  e = launch_dep(sort_kern, dim3(unsigned(p.n_windows)), dim3(kSortTpb), sort_smem, stream, keys, nrows, nk,
+                 p.window_rows, perm, offs, counter);
   if (e != cudaSuccess) return e;
 
   // 2. rows per (group, key), unit tables and the list of keys to fold
-  rbk_units_kernel<1024><<<unsigned(p.n_groups), 1024, 0, stream>>>(offs, p.n_windows, p.group, gcnt, nk, p.max_units,
-                                                                    rbk_unit_cap(nrows), uoffs, ukey, ufirst, ulen,
-                                                                    fold_list, counter + 1);
-  e = cudaGetLastError();
+  e = launch_dep(rbk_units_kernel<1024>, dim3(unsigned(p.n_groups)), dim3(1024), 0, stream, offs, p.n_windows, p.group,
+                 gcnt, nk, p.max_units, rbk_unit_cap(nrows), uoffs, ukey, ufirst, ulen, fold_list, counter + 1);
   if (e != cudaSuccess) return e;
 
   // 4. stream the matrix, one warp per (unit, part of the columns)
@@ -746,9 +748,9 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
       --split;                                                                                               \
     if (split < 1) split = 1;                                                                                \
     if (ctas > ceil_div<int64_t>(slots * split, 8)) ctas = ceil_div<int64_t>(slots * split, 8);              \
-    kern<<<unsigned(ctas), 256, 0, stream>>>(partial, A, lda, weights, int(ncols), nk, p.window_rows,        \
-                                             p.n_windows, p.group, p.n_groups, p.max_units, G, int(split),   \
-                                             perm, offs, uoffs, ukey, ufirst, ulen, counter);                \
+    (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(256), 0, stream, partial, A, lda, weights, int(ncols), \
+                     nk, p.window_rows, p.n_windows, p.group, p.n_groups, p.max_units, G, int(split), perm,  \
+                     offs, uoffs, ukey, ufirst, ulen, counter);                                              \
   } while (0)
   if (p.vec > 1) {
     B2R_LAUNCH_STREAM(V16);
@@ -763,14 +765,14 @@ cudaError_t launch_rows_by_key_sorted(SumT* sums,
   int64_t fold_ctas = ceil_div<int64_t>(p.max_fold, 8);
   if (fold_ctas > int64_t(sms) * 8) fold_ctas = int64_t(sms) * 8;
   if (fold_ctas < 1) fold_ctas = 1;
-  rbk_fold_kernel<SumT><<<unsigned(fold_ctas), 256, 0, stream>>>(partial, uoffs, fold_list, counter + 1, p.max_units,
-                                                                 int(ncols), nk);
+  (void)launch_dep(rbk_fold_kernel<SumT>, dim3(unsigned(fold_ctas)), dim3(256), 0, stream, partial, uoffs, fold_list,
+                   counter + 1, p.max_units, int(ncols), nk);
   if (nkeys <= 2048) {  // few keys: a CTA per key
-    rbk_merge_kernel<SumT, 8><<<unsigned(nkeys), 256, 0, stream>>>(
-      sums, counts, partial, gcnt, uoffs, p.n_groups, p.max_units, int(ncols), nk, reset);
+    (void)launch_dep(rbk_merge_kernel<SumT, 8>, dim3(unsigned(nkeys)), dim3(256), 0, stream, sums, counts, partial,
+                     gcnt, uoffs, p.n_groups, p.max_units, int(ncols), nk, reset);
   } else {
-    rbk_merge_kernel<SumT, 1><<<unsigned(ceil_div<int64_t>(nkeys, 8)), 256, 0, stream>>>(
-      sums, counts, partial, gcnt, uoffs, p.n_groups, p.max_units, int(ncols), nk, reset);
+    (void)launch_dep(rbk_merge_kernel<SumT, 1>, dim3(unsigned(ceil_div<int64_t>(nkeys, 8))), dim3(256), 0, stream, sums,
+                     counts, partial, gcnt, uoffs, p.n_groups, p.max_units, int(ncols), nk, reset);
   }
   return cudaGetLastError();
 }
