@@ -471,3 +471,30 @@ def test_bad_arguments(cuda):
     d = L.ReduceDesc(n_rows=4, n_cols=5)
     assert lib.b2r_reduce(d, None, t.data_ptr(), None, 0, None) == L.ERR_BAD_ARG
     torch.cuda.synchronize()
+
+
+def test_dependent_launches_change_no_result(cuda, knobs):
+    """The hot kernels are launched with programmatic stream serialization (a kernel may be scheduled while its
+    predecessor drains and waits for it before touching global memory). Back-to-back calls that feed one another,
+    with the feature on and off (B2R_DEP_LAUNCH=2), must give the same bits."""
+    a, _ = device_synth((200000, 64), np.float32, 3, "uniform", -1, 1, cuda)
+    keys, _ = device_synth((200000,), np.int32, 4, "int", 0, 100, cuda)
+
+    def chain():
+        col = linalg.reduce(a, linalg.ALONG_COLUMNS)                       # two launches
+        row = linalg.reduce(a, linalg.ALONG_ROWS, main_op="sq", final_op="sqrt")
+        nrm = linalg.row_normalize(a, "L2")
+        col2 = linalg.reduce(nrm, linalg.ALONG_COLUMNS)                    # reads what the previous call wrote
+        byk = linalg.reduce_rows_by_key(nrm, keys, 100)                    # five launches
+        tot = linalg.reduce(byk.reshape(1, -1), linalg.ALONG_ROWS)
+        return [col, row, nrm, col2, byk, tot]
+
+    on = [t.clone() for t in chain()]
+    for _ in range(3):  # again, back to back, into fresh outputs
+        again = chain()
+    torch.cuda.synchronize(cuda)
+    knobs(B2R_DEP_LAUNCH="2")
+    off = chain()
+    for x, y, z in zip(on, again, off):
+        assert torch.equal(x, y)
+        assert torch.equal(x, z)
