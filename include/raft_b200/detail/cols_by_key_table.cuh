@@ -7,8 +7,9 @@
 // the same for every row, so a LANE takes a ROW of the tile and the warp walks the columns: the accumulator of
 // (key, row) lives in shared memory at table[warp][key][lane] - the bank is the lane, whatever the key, so the
 // read-add-write of an element never conflicts and needs no atomic: the cell belongs to one lane. Per element
-// that is a key extraction, an address, two loads, an add and a store - about 7.5 lane-instructions whatever the
-// number of keys (the lane-per-segment kernel: 24 with 128 keys).
+// that is a key extraction, an address, two loads, an add and a store - 10 lane-instructions as compiled, whatever
+// the number of keys (the lane-per-segment kernel: 24 with 128 keys). Measured, fp32 2000 x 200000: 64 keys 6.1
+// TB/s, 128 keys 5.7, 255 keys 4.6.
 //
 //  * Tiles are boxes of 32 rows x 228 columns fetched by ONE tiled-TMA instruction each (a ring of bulk row
 //    copies is bound by the number of copies, and 32 pieces of 912 bytes would be far too many); 228 because
