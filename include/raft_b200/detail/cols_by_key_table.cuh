@@ -11,12 +11,13 @@
 // the number of keys (the lane-per-segment kernel: 24 with 128 keys). Measured, fp32 2000 x 200000: 64 keys 6.1
 // TB/s, 128 keys 5.7, 255 keys 4.6.
 //
-//  * Tiles are boxes of 32 rows x 228 columns fetched by ONE tiled-TMA instruction each (a ring of bulk row
-//    copies is bound by the number of copies, and 32 pieces of 912 bytes would be far too many); 228 because
-//    the box lands densely in shared memory and a pitch of 228 words = 4 (mod 32) lets lane r, which reads row
-//    r, avoid its neighbours: the lanes of a warp are four groups of eight rows, group g reads column
-//    4m + (g + s) % 4 in step s of column group m, so a step touches banks 4 (r % 8) + (g + s) % 4 - all 32
-//    different - and after four steps every lane has seen the four columns of the group.
+//  * Tiles are boxes of 32 rows x 228 columns (188 where only that leaves room for a fourth stage beside the
+//    tables) fetched by ONE tiled-TMA instruction each (a ring of bulk row copies is bound by the number of
+//    copies, and 32 pieces of 912 bytes would be far too many); 228 because the box lands densely in shared
+//    memory and a pitch of 4 (mod 8) words lets lane r, which reads row r, avoid its neighbours: the lanes of a
+//    warp are four groups of eight rows, group g reads column 4m + (g + s) % 4 in step s of column group m, so a
+//    step touches 32 different banks (eight multiples of four from r % 8, plus (g + s) % 4), and after four steps
+//    every lane has seen the four columns of the group.
 //  * Keys travel as one byte per column (cbk_keys8_kernel: key, or the dummy slot `nkeys` for a key outside
 //    [0, nkeys) and for the columns past the end), 240 bytes per box beside it in the stage; a lane fetches the
 //    four keys of a column group with one broadcast load.
@@ -42,14 +43,14 @@ namespace raft_b200 {
 namespace detail {
 
 constexpr int kCbkTableRows    = 32;                  // rows of a box: one per lane
-constexpr int kCbkTableCols    = 228;                 // columns of a box; 228 words = 4 (mod 32)
-constexpr int kCbkTableGroups  = kCbkTableCols / 4;   // 57 column groups
+constexpr int kCbkTableCols    = 228;                 // columns of a box; 228 words = 4 (mod 8): see above
+constexpr int kCbkTableColsNarrow = 188;              // ... when only the narrower box leaves room for four stages
 constexpr int kCbkTableKeyB    = 240;                 // key bytes per box, a multiple of 16
 constexpr int kCbkTableDupByte = 232;                // first of the 8 bytes of duplicate flags in them
 constexpr int kCbkTableMaxKeys = 255;                 // keys and the dummy slot fit a byte
 constexpr int kCbkTableMaxAdds = 128;                 // fp32 additions into one cell between flushes
 constexpr int kCbkTableMaxStages = 6;
-constexpr size_t kCbkTableBoxBytes = size_t(kCbkTableRows) * kCbkTableCols * sizeof(float);  // 29184
+constexpr size_t cbk_table_box_bytes(int cols) { return size_t(kCbkTableRows) * size_t(cols) * sizeof(float); }
 
 B2R_DI float lds_f32(uint32_t addr)
 {
@@ -104,7 +105,8 @@ B2R_DI void table_add_pair(uint32_t a0, float x0, uint32_t a1, float x1)
 
 struct CbkTablePlan {
   bool ok;
-  int warps;   // consumer warps: 8 up to 128 keys, 4 above
+  int warps;   // consumer warps: 8 while their tables leave room for three stages, 4 above
+  int cols;    // columns of a box: 228, or 188 when that makes room for a fourth stage
   int stages;
   int n_chunks;
   int y_split;
@@ -124,20 +126,32 @@ inline CbkTablePlan plan_cols_by_key_table(const T* data, int64_t nrows, int64_t
   if (!std::is_same<T, float>::value || nkeys < 1 || nkeys > kCbkTableMaxKeys || nrows < 1 ||
       ncols < kCbkTableCols || ncols % 4 != 0 || !aligned16(data) || ncols > (int64_t(1) << 30))
     return p;
-  p.warps       = nkeys <= 128 ? 8 : 4;
+  p.cols = kCbkTableCols;
+  p.warps       = nkeys <= tuning().colkey_table_w8_max ? 8 : 4;
   p.table_bytes = size_t(nkeys + 1) * 32 * sizeof(float);
-  p.stage_bytes = align_up(kCbkTableBoxBytes + kCbkTableKeyB, 128);
   const size_t budget = size_t(224) << 10;
   const size_t tables = size_t(p.warps) * p.table_bytes;
-  if (tables + 2 * p.stage_bytes > budget) return p;
-  int st   = int((budget - tables) / p.stage_bytes);
+  auto stages_with    = [&](int cols) {
+    const size_t sb = align_up(cbk_table_box_bytes(cols) + kCbkTableKeyB, 128);
+    return tables + 2 * sb > budget ? 0 : int((budget - tables) / sb);
+  };
+  // three stages of the wide box are what fits beside the eight tables of 128 keys; the narrow box makes it four
+  // (measured: 128 keys 5.68 -> 5.91 TB/s, 112 keys 5.62 -> 5.89; two stages instead of three cost a fifth; with
+  // four consumer warps the stage count does not matter, they are what bounds the kernel)
+  const int knob = tuning().colkey_table_cols;
+  if (knob == kCbkTableColsNarrow ||
+      (knob == 0 && p.warps == 8 && stages_with(kCbkTableCols) < 4 && stages_with(kCbkTableColsNarrow) >= 4))
+    p.cols = kCbkTableColsNarrow;
+  p.stage_bytes = align_up(cbk_table_box_bytes(p.cols) + kCbkTableKeyB, 128);
+  int st        = stages_with(p.cols);
+  if (st < 2) return p;
   p.stages = st > kCbkTableMaxStages ? kCbkTableMaxStages : st;
   p.smem   = tables + size_t(p.stages) * p.stage_bytes;
-  p.n_chunks    = int(ceil_div<int64_t>(ncols, kCbkTableCols));
+  p.n_chunks    = int(ceil_div<int64_t>(ncols, p.cols));
   p.n_row_tiles = ceil_div<int64_t>(nrows, kCbkTableRows);
   if (p.n_row_tiles > int64_t(0x7fffffff) / kCbkTableRows) return p;
   // columns between two flushes of a table: at most kCbkTableMaxAdds additions into a cell on average
-  const int64_t max_cpc = std::max<int64_t>(1, int64_t(kCbkTableMaxAdds) * p.warps * nkeys / kCbkTableCols);
+  const int64_t max_cpc = std::max<int64_t>(1, int64_t(kCbkTableMaxAdds) * p.warps * nkeys / p.cols);
   int y_min             = int(ceil_div<int64_t>(p.n_chunks, max_cpc));
   if (int64_t(y_min) > 65535) return p;
   const int y_knob = tuning().colkey_table_y;  // experiments: this many column splits at least
@@ -189,22 +203,23 @@ __global__ void __launch_bounds__(256) cbk_keys8_kernel(unsigned char* __restric
                                                        const KeyT* __restrict__ keys,
                                                        int64_t ncols,
                                                        int nkeys,
-                                                       int n_chunks)
+                                                       int n_chunks,
+                                                       int cols)
 {
   grid_dep_sync();
   const int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
   if (i >= int64_t(n_chunks) * kCbkTableKeyB) return;
   const int ch     = int(i / kCbkTableKeyB);
   const int j      = int(i - int64_t(ch) * kCbkTableKeyB);
-  const int64_t c0 = int64_t(ch) * kCbkTableCols;
+  const int64_t c0 = int64_t(ch) * cols;
   int v            = nkeys;
-  if (j < kCbkTableCols) {
+  if (j < cols) {
     v = cbk_table_key(keys, c0 + j, ncols, nkeys);
   } else if (j >= kCbkTableDupByte) {
     v = 0;
     for (int b = 0; b < 8; ++b) {
       const int m = (j - kCbkTableDupByte) * 8 + b;
-      if (m >= kCbkTableGroups) break;
+      if (m >= cols / 4) break;
       const int k0 = cbk_table_key(keys, c0 + 4 * m, ncols, nkeys), k1 = cbk_table_key(keys, c0 + 4 * m + 1, ncols, nkeys);
       const int k2 = cbk_table_key(keys, c0 + 4 * m + 2, ncols, nkeys), k3 = cbk_table_key(keys, c0 + 4 * m + 3, ncols, nkeys);
       if (k0 == k1 || k0 == k2 || k0 == k3 || k1 == k2 || k1 == k3 || k2 == k3) v |= 1 << b;
@@ -213,7 +228,7 @@ __global__ void __launch_bounds__(256) cbk_keys8_kernel(unsigned char* __restric
   keys8[i] = static_cast<unsigned char>(v);
 }
 
-template <typename T, int W>
+template <typename T, int W, int COLS>
 __global__ void __launch_bounds__(W * 32 + 32, 1) cbk_table_kernel(T* __restrict__ out,
                                                                  double* __restrict__ partial,
                                                                  const __grid_constant__ CUtensorMap tmap,
@@ -226,7 +241,12 @@ __global__ void __launch_bounds__(W * 32 + 32, 1) cbk_table_kernel(T* __restrict
 {
   extern __shared__ __align__(128) unsigned char smem_tma[];
   constexpr int n_cons      = W * 32;
-  constexpr int GPW         = (kCbkTableGroups + W - 1) / W;  // column groups of a box per warp, at most
+  constexpr int NG          = COLS / 4;            // column groups of a box
+  constexpr int NC          = NG / W;              // groups every warp has
+  constexpr int EX          = NG % W;              // the first EX warps have one more
+  constexpr int GPW         = NC + (EX != 0 ? 1 : 0);
+  constexpr size_t kBoxBytes = cbk_table_box_bytes(COLS);
+  static_assert(COLS % 8 == 4 && COLS + 8 <= kCbkTableDupByte + 8 && GPW <= 16, "pitch = 4 (mod 8) words; flags behind the keys");
   unsigned char* stages     = smem_tma + size_t(W) * P.table_bytes;
   const uint32_t tables_u32 = smem_u32(smem_tma);
   const uint32_t stages_u32 = smem_u32(stages);
@@ -280,9 +300,9 @@ __global__ void __launch_bounds__(W * 32 + 32, 1) cbk_table_kernel(T* __restrict
           }
           const int ch      = ch0 + c * ch_step;
           unsigned char* st = stages + size_t(s) * P.stage_bytes;
-          mbar_expect_tx(&s_full[s], unsigned(kCbkTableBoxBytes) + unsigned(kCbkTableKeyB));  // zero fill included
-          tma_load_2d(st, &tmap, ch * kCbkTableCols, int(rti * kCbkTableRows), &s_full[s]);
-          bulk_load(st + kCbkTableBoxBytes, keys8 + size_t(ch) * kCbkTableKeyB, unsigned(kCbkTableKeyB), &s_full[s]);
+          mbar_expect_tx(&s_full[s], unsigned(kBoxBytes) + unsigned(kCbkTableKeyB));  // zero fill included
+          tma_load_2d(st, &tmap, ch * COLS, int(rti * kCbkTableRows), &s_full[s]);
+          bulk_load(st + kBoxBytes, keys8 + size_t(ch) * kCbkTableKeyB, unsigned(kCbkTableKeyB), &s_full[s]);
           ++issued;
         }
       }
@@ -303,15 +323,15 @@ __global__ void __launch_bounds__(W * 32 + 32, 1) cbk_table_kernel(T* __restrict
   const int warp = tid >> 5;
   const int grp  = lane >> 3;  // which of the four columns of a group this lane reads first
   // this warp's column groups of every box
-  static_assert(kCbkTableGroups == W * (GPW - 1) + 1, "GPW - 1 groups per warp and one more for the last warp");
-  const int g0 = warp * (GPW - 1);
+  const int g0         = warp * NC + (warp < EX ? warp : EX);
+  const bool has_extra = warp < EX;
   const uint32_t cell0 = tables_u32 + uint32_t(warp) * uint32_t(P.table_bytes) + uint32_t(lane) * 4u;  // (key 0, lane)
   unsigned sel[4], dcol[4];
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
     const unsigned q = unsigned(grp + s) & 3u;
     sel[s]           = q | 0x4440u;  // byte q of the four keys, zero-extended
-    dcol[s]          = uint32_t(lane) * uint32_t(kCbkTableCols * sizeof(float)) + q * 4u + 16u * unsigned(g0);
+    dcol[s]          = uint32_t(lane) * uint32_t(COLS * sizeof(float)) + q * 4u + 16u * unsigned(g0);
   }
 
   long long seq = 0;
@@ -330,29 +350,29 @@ __global__ void __launch_bounds__(W * 32 + 32, 1) cbk_table_kernel(T* __restrict
         continue;
       }
       const uint32_t st   = stages_u32 + uint32_t(s) * uint32_t(P.stage_bytes);
-      const uint32_t keys = st + uint32_t(kCbkTableBoxBytes) + 4u * unsigned(g0);
+      const uint32_t keys = st + uint32_t(kBoxBytes) + 4u * unsigned(g0);
       const uint32_t rb0 = st + dcol[0], rb1 = st + dcol[1], rb2 = st + dcol[2], rb3 = st + dcol[3];
       // the keys of all groups of the warp and the duplicate flags first: one latency per box, not per group
       unsigned kk[GPW];
-      static_for<GPW>([&](auto jc) { kk[decltype(jc)::value] = lds_u32_at<4 * decltype(jc)::value>(keys); });  // (the last one is used by the last warp only)
-      const unsigned dlo = lds_u32(st + uint32_t(kCbkTableBoxBytes) + uint32_t(kCbkTableDupByte));
-      const unsigned dhi = lds_u32(st + uint32_t(kCbkTableBoxBytes) + uint32_t(kCbkTableDupByte) + 4u);
+      static_for<GPW>([&](auto jc) { kk[decltype(jc)::value] = lds_u32_at<4 * decltype(jc)::value>(keys); });  // (the last one only counts for a warp with an extra group)
+      const unsigned dlo = lds_u32(st + uint32_t(kBoxBytes) + uint32_t(kCbkTableDupByte));
+      const unsigned dhi = lds_u32(st + uint32_t(kBoxBytes) + uint32_t(kCbkTableDupByte) + 4u);
       const unsigned dup = unsigned(((static_cast<unsigned long long>(dhi) << 32) | dlo) >> g0);
       float x[2][4];
       x[0][0] = lds_f32(rb0);
       x[0][1] = lds_f32(rb1);
       x[0][2] = lds_f32(rb2);
       x[0][3] = lds_f32(rb3);
-      // every warp has GPW - 1 groups, the last warp one more (57 = 8 x 7 + 1 = 4 x 14 + 1). Two copies of the
+      // every warp has NC groups, the first EX warps one more (57 = 8 x 7 + 1, 47 = 8 x 5 + 7). Two copies of the
       // walk: when no group of the warp has two columns of one key (7 boxes of 10 with 128 keys) the first runs,
       // straight-line code that adds the four columns of a group all at once; a branch per group would cost
       // three control instructions per four elements.
-      const unsigned mine = warp == W - 1 ? (1u << GPW) - 1u : (1u << (GPW - 1)) - 1u;
+      const unsigned mine = has_extra ? (1u << GPW) - 1u : (1u << NC) - 1u;
       auto walk = [&](auto fast_c) {
         constexpr bool kFast = decltype(fast_c)::value;
         static_for<GPW>([&](auto jc) {
           constexpr int j = decltype(jc)::value;
-          if (j < GPW - 1 || warp == W - 1) {
+          if (j < NC || has_extra) {
             const float* xc = x[j & 1];
             if constexpr (j + 1 < GPW) {  // the next group's elements are on their way while this one is added
               float* xn = x[(j + 1) & 1];
@@ -434,7 +454,7 @@ cudaError_t launch_cols_by_key_table(T* out,
     return cudaSuccess;
   } else {
     CUtensorMap tmap;
-    if (make_tensor_map_2d<float>(&tmap, data, nrows, ncols, ncols, kCbkTableRows, kCbkTableCols) != cudaSuccess) {
+    if (make_tensor_map_2d<float>(&tmap, data, nrows, ncols, ncols, kCbkTableRows, p.cols) != cudaSuccess) {
       *unavailable = true;  // no tensor map (driver entry point missing): the caller takes another form
       return cudaSuccess;
     }
@@ -446,10 +466,12 @@ cudaError_t launch_cols_by_key_table(T* out,
     const int nk         = int(nkeys);
     const int64_t nb     = int64_t(p.n_chunks) * kCbkTableKeyB;
     (void)launch_dep(cbk_keys8_kernel<KeyT>, dim3(unsigned(ceil_div<int64_t>(nb, 256))), dim3(256), 0, stream, keys8,
-                     keys, ncols, nk, p.n_chunks);
+                     keys, ncols, nk, p.n_chunks, p.cols);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    auto kern = p.warps == 8 ? cbk_table_kernel<T, 8> : cbk_table_kernel<T, 4>;
+    auto kern = p.cols == kCbkTableCols
+                  ? (p.warps == 8 ? cbk_table_kernel<T, 8, kCbkTableCols> : cbk_table_kernel<T, 4, kCbkTableCols>)
+                  : (p.warps == 8 ? cbk_table_kernel<T, 8, kCbkTableColsNarrow> : cbk_table_kernel<T, 4, kCbkTableColsNarrow>);
     e         = ensure_dynamic_smem(kern, p.smem);
     if (e != cudaSuccess) return e;
     const dim3 grid{unsigned(ceil_div<int64_t>(p.n_row_tiles, p.row_tiles_per_cta)), unsigned(p.y_split), 1u};

@@ -125,6 +125,8 @@ struct Tuning {
   int colkey32_ch          = 0;     // B2R_COLKEY32_CH columns per chunk of the walk form of the keyed column sums (0: the longest that fits)
   int colkey32_rt          = 16;    // B2R_COLKEY32_RT rows per tile of that form: 8, 16 or 32
   int colkey_walk_max_keys = 40;    // B2R_COLKEY_WALK_MAX most keys for which that form is chosen by itself (fp32: the table form takes over)
+  int colkey_table_cols    = 0;     // B2R_COLKEY_TABLE_COLS columns of a box of the table form: 228, 188 (0: the narrow one when it makes room for a fourth stage)
+  int colkey_table_w8_max  = 136;   // B2R_COLKEY_TABLE_W8 most keys with eight consumer warps (their tables leave room for fewer stages)
   int colkey_table_y       = 0;     // B2R_COLKEY_TABLE_Y column splits of the table form (0: planned)
   int colkey_table_max_keys = 255;  // B2R_COLKEY_TABLE_MAX_KEYS most keys for the table form of the keyed column sums (fp32)
   int colkey_tma           = 1;     // B2R_COLKEY_TMA 1: TMA-staged ring for the sorted column tiles, 2: off
@@ -179,6 +181,8 @@ inline Tuning read_tuning_from_env()
   x.colkey32_ch          = env_int("B2R_COLKEY32_CH", x.colkey32_ch);
   x.colkey32_rt          = env_int("B2R_COLKEY32_RT", x.colkey32_rt);
   x.colkey_walk_max_keys = env_int("B2R_COLKEY_WALK_MAX", x.colkey_walk_max_keys);
+  x.colkey_table_cols    = env_int("B2R_COLKEY_TABLE_COLS", x.colkey_table_cols);
+  x.colkey_table_w8_max  = env_int("B2R_COLKEY_TABLE_W8", x.colkey_table_w8_max);
   x.colkey_table_y       = env_int("B2R_COLKEY_TABLE_Y", x.colkey_table_y);
   x.colkey_table_max_keys = env_int("B2R_COLKEY_TABLE_MAX_KEYS", x.colkey_table_max_keys);
   x.colkey_tma           = env_int("B2R_COLKEY_TMA", x.colkey_tma);
