@@ -2,10 +2,11 @@
 //
 // Counterpart of the reference's cached / direct kernels
 // (linalg/detail/reduce_cols_by_key.cuh:23-68, dispatch :89-138). Two algorithms:
-//  * sorted column tiles for large inputs with up to a few hundred keys: no floating-point atomics,
-//    tiles staged by bulk copies - with a warp walking the sorted columns of its keys (cols_by_key_walk.cuh) for matrices of at least
-//    256 rows and up to 64 keys, with a lane per (row, key) segment (cols_by_key_sorted.cuh) otherwise; fp32 with 65 to
-//    255 keys skips the sort and keeps a table cell per (key, row) and warp in shared memory (cols_by_key_table.cuh);
+//  * staged tiles for large inputs with up to a few hundred keys, no floating-point atomics: sorted column tiles
+//    with a warp walking the sorted columns of its keys (cols_by_key_walk.cuh) for matrices of at least 256 rows
+//    and up to 32 keys (64 for types other than fp32), a table cell per (key, row) and warp in shared memory
+//    without any sort (cols_by_key_table.cuh) for fp32 with 33 to 255 keys, sorted column tiles with a lane per
+//    (row, key) segment (cols_by_key_sorted.cuh) otherwise;
 //  * the kernels of this file otherwise: a CTA owns a tile of RT rows and a contiguous range of
 //    columns, accumulates into a privatised [RT x nkeys] table in shared memory (shared-memory
 //    atomics; lanes of a warp read 128 contiguous bytes of one row per step) and flushes the

@@ -1,4 +1,4 @@
-// Keyed column sums, "table" form for 65 to 255 keys (fp32):
+// Keyed column sums, "table" form for 33 to 255 keys (fp32):
 //     out[r][keys[c]] += data[r][c]          data row-major [nrows x ncols], rows on 16-byte boundaries
 //
 // With many keys a chunk of columns holds only a few columns per key, and the two sorted forms
@@ -9,10 +9,10 @@
 // read-add-write of an element never conflicts and needs no atomic: the cell belongs to one lane. Per element
 // that is a key extraction, an address, two loads, an add and a store - 10 lane-instructions as compiled, whatever
 // the number of keys (the lane-per-segment kernel: 24 with 128 keys). Measured, fp32 2000 x 200000: 64 keys 6.1
-// TB/s, 128 keys 5.7, 255 keys 4.6.
+// TB/s, 128 keys 5.9, 255 keys 4.6.
 //
-//  * Tiles are boxes of 32 rows x 228 columns (188 where only that leaves room for a fourth stage beside the
-//    tables) fetched by ONE tiled-TMA instruction each (a ring of bulk row copies is bound by the number of
+//  * Tiles are boxes of 32 rows x 228 columns (188 with eight consumer warps: more stages beside the tables)
+//    fetched by ONE tiled-TMA instruction each (a ring of bulk row copies is bound by the number of
 //    copies, and 32 pieces of 912 bytes would be far too many); 228 because the box lands densely in shared
 //    memory and a pitch of 4 (mod 8) words lets lane r, which reads row r, avoid its neighbours: the lanes of a
 //    warp are four groups of eight rows, group g reads column 4m + (g + s) % 4 in step s of column group m, so a
@@ -44,7 +44,7 @@ namespace detail {
 
 constexpr int kCbkTableRows    = 32;                  // rows of a box: one per lane
 constexpr int kCbkTableCols    = 228;                 // columns of a box; 228 words = 4 (mod 8): see above
-constexpr int kCbkTableColsNarrow = 188;              // ... when only the narrower box leaves room for four stages
+constexpr int kCbkTableColsNarrow = 188;              // ... of the narrow box (eight consumer warps)
 constexpr int kCbkTableKeyB    = 240;                 // key bytes per box, a multiple of 16
 constexpr int kCbkTableDupByte = 232;                // first of the 8 bytes of duplicate flags in them
 constexpr int kCbkTableMaxKeys = 255;                 // keys and the dummy slot fit a byte
@@ -135,12 +135,12 @@ inline CbkTablePlan plan_cols_by_key_table(const T* data, int64_t nrows, int64_t
     const size_t sb = align_up(cbk_table_box_bytes(cols) + kCbkTableKeyB, 128);
     return tables + 2 * sb > budget ? 0 : int((budget - tables) / sb);
   };
-  // three stages of the wide box are what fits beside the eight tables of 128 keys; the narrow box makes it four
-  // (measured: 128 keys 5.68 -> 5.91 TB/s, 112 keys 5.62 -> 5.89; two stages instead of three cost a fifth; with
-  // four consumer warps the stage count does not matter, they are what bounds the kernel)
+  // With eight consumer warps the narrow box: more, smaller stages for the same bytes in flight, and four stages
+  // instead of three beside the tables of 128 keys (measured, 228 / 188 columns: 64 keys 5.93 / 6.08 TB/s, 100
+  // keys 6.05 / 6.14, 128 keys 5.65 / 5.9; 148 columns lose - 5.3 to 5.6 - their row pieces are too short; two
+  // stages instead of three cost a fifth). With four warps the stages do not matter: the warps bound the kernel.
   const int knob = tuning().colkey_table_cols;
-  if (knob == kCbkTableColsNarrow ||
-      (knob == 0 && p.warps == 8 && stages_with(kCbkTableCols) < 4 && stages_with(kCbkTableColsNarrow) >= 4))
+  if (knob == kCbkTableColsNarrow || (knob == 0 && p.warps == 8 && stages_with(kCbkTableColsNarrow) >= 4))
     p.cols = kCbkTableColsNarrow;
   p.stage_bytes = align_up(cbk_table_box_bytes(p.cols) + kCbkTableKeyB, 128);
   int st        = stages_with(p.cols);

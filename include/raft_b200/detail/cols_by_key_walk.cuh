@@ -12,10 +12,11 @@
 // Tiles are RT rows x CH columns with FEW, LONG row pieces (16 x 1024 by default): what bounds a ring of bulk
 // copies is their number, not their bytes - 32 pieces of 2 KB per tile ran at the same tiles per second as 32
 // pieces of 1 KB (5.4 against 2.9 TB/s with 8 keys).
-// Measured, fp32 2000 x 200000, TB/s (this form / lane per segment): 8 keys 6.5 / 5.5, 32 keys 6.1 / 4.8, 64 keys
-// 4.9 / 4.5, 128 keys 3.4 / 4.15, 256 keys 2.2 / 3.75 - with many keys a warp owns many short segments per tile
-// and pays a chain of shared-memory latencies for each, so the host takes this form up to 64 keys. (With fp32
-// partial sums it is 1-10 % faster, but then a repeated call can differ in the last bit: see the walk below.)
+// Measured, fp32 2000 x 200000, TB/s (this form / lane per segment): 8 keys 6.7 / 5.5, 32 keys 6.4 / 4.8, 64 keys
+// 5.3 / 4.5, 128 keys 3.4 / 4.15, 256 keys 2.2 / 3.75 - with many keys a warp owns many short segments per tile
+// and pays a chain of shared-memory latencies for each, so the host takes this form up to 32 keys (64 for
+// fp64, which the table form of cols_by_key_table.cuh does not take). (With fp32 partial sums it is 1-10 %
+// faster, but then a repeated call can differ in the last bit: see the walk below.)
 // Nothing else changes: the columns are counting-sorted by key once per call, chunk by chunk (cbk_sort_kernel),
 // a producer WARP streams the RT row pieces of a tile (one bulk copy per lane), the chunk's sorted offsets and
 // its segment starts into a ring of shared-memory stages, one CTA per SM walks a range of row tiles x a range

@@ -124,7 +124,7 @@ struct Tuning {
   int colkey_algo          = 0;     // B2R_COLKEY_ALGO 0: auto, 1: shared-memory atomics, 2: sorted tiles, a lane per segment, 3: sorted tiles, a warp walking its keys, 4: table cells (fp32, up to 255 keys)
   int colkey32_ch          = 0;     // B2R_COLKEY32_CH columns per chunk of the walk form of the keyed column sums (0: the longest that fits)
   int colkey32_rt          = 16;    // B2R_COLKEY32_RT rows per tile of that form: 8, 16 or 32
-  int colkey_walk_max_keys = 40;    // B2R_COLKEY_WALK_MAX most keys for which that form is chosen by itself (fp32: the table form takes over)
+  int colkey_walk_max_keys = 32;    // B2R_COLKEY_WALK_MAX most keys for which that form is chosen by itself (fp32: the table form takes over)
   int colkey_table_cols    = 0;     // B2R_COLKEY_TABLE_COLS columns of a box of the table form: 228, 188 (0: the narrow one when it makes room for a fourth stage)
   int colkey_table_w8_max  = 136;   // B2R_COLKEY_TABLE_W8 most keys with eight consumer warps (their tables leave room for fewer stages)
   int colkey_table_y       = 0;     // B2R_COLKEY_TABLE_Y column splits of the table form (0: planned)
