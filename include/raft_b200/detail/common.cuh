@@ -63,13 +63,15 @@ struct vec16 {
 };
 
 // Programmatic dependent launch. A kernel launched with launch_dep() (launch.cuh) may be scheduled while the
-// previous kernel of the stream is still draining: it announces first that ITS successor may be scheduled
-// likewise, then waits until the predecessor has completed and its writes are visible. Everything before the
-// wait must stay off global memory. Both instructions do nothing in a kernel launched the ordinary way.
+// previous kernel of the stream is still draining: it waits until the predecessor has completed and its writes
+// are visible, and only THEN announces that its own successor may be scheduled likewise - one level of overlap.
+// (Announcing first lets a grandchild become resident while the grandparent still runs: measured on the five
+// kernels of the keyed row sums with 4096 keys, that cost 110 us of 830.) Everything before the wait must stay
+// off global memory. Both instructions do nothing in a kernel launched the ordinary way.
 B2R_DI void grid_dep_sync()
 {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // Streaming load: the matrix is read exactly once, so it bypasses L1 allocation
