@@ -153,7 +153,7 @@ struct Tuning {
   int row_split_ring       = 1;     // B2R_ROW_SPLIT_RING 1: ring of bulk copies for a handful of very long rows, 2: off
   int row_split_ring_min_mb = 64;   // B2R_ROW_SPLIT_RING_MB shortest row (MiB) that takes it
   int dep_launch           = 1;     // B2R_DEP_LAUNCH 1: kernels that begin with grid_dep_sync() are launched with programmatic stream serialization, 2: ordinary launches
-  int normalize_ctas_per_sm = 0;    // B2R_NORMALIZE_CPS row_normalize CTAs per SM at most (0: twice the resident number)
+  int normalize_ctas_per_sm = 0;    // B2R_NORMALIZE_CPS row_normalize CTAs per SM at most (0: 256, short-lived CTAs; 8: two resident waves)
   int wait_limit_ms        = 1000;  // B2R_WAIT_LIMIT_MS bound of every mbarrier wait inside the ring kernels, milliseconds
   int test_skip_tile       = 0;     // B2R_TEST_SKIP_TILE test hook: the producer of the first CTA never requests tile (value - 1)
 };

@@ -322,7 +322,8 @@ cudaError_t launch_row_normalize(T* out,
     const int G      = int(g > 32u ? 32u : g);                                                            \
     const int64_t rows_per_cta = int64_t(32 / G) * U_ * 8;                                                \
     int64_t ctas               = ceil_div<int64_t>(n_rows, rows_per_cta);                                 \
-    const int64_t cap          = int64_t(sms) * (tuning().normalize_ctas_per_sm > 0 ? tuning().normalize_ctas_per_sm : occ * 2); \
+    (void)occ;                                                                                            \
+    const int64_t cap = int64_t(sms) * (tuning().normalize_ctas_per_sm > 0 ? tuning().normalize_ctas_per_sm : 256); \
     if (ctas > cap) ctas = cap;                                                                           \
     (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(256), 0, stream,                                                \
                      out, in, n_rows, n_cols, init, eps, main_op, reduce_op,                                          \
@@ -333,7 +334,11 @@ cudaError_t launch_row_normalize(T* out,
     auto kern      = row_normalize_cta_kernel<T, IdxT, MainOp, ReduceOp, FinalOp, VEC_, CPT_>;            \
     static int occ = resident_ctas(kern, 256, 0);                                                         \
     int64_t ctas   = n_rows;                                                                              \
-    if (ctas > int64_t(sms) * occ * 2) ctas = int64_t(sms) * occ * 2;                                     \
+    (void)occ;                                                                                            \
+    {                                                                                                     \
+      const int64_t cap = int64_t(sms) * (tuning().normalize_ctas_per_sm > 0 ? tuning().normalize_ctas_per_sm : 256); \
+      if (ctas > cap) ctas = cap;                                                                         \
+    }                                                                                                     \
     (void)launch_dep(kern, dim3(unsigned(ctas)), dim3(256), 0, stream,                                                \
                      out, in, n_rows, n_cols, init, eps, main_op, reduce_op,                                          \
                                              final_op);                                                   \
