@@ -116,6 +116,7 @@ struct Tuning {
   int row_chunk_threshold  = 4;   // B2R_ROW_CHUNK rows with >= this many passes per lane use kChunks
   int row_cpl              = 0;   // B2R_ROW_CPL   chunks of a row per lane and pass: 1, 2, 4 (0: by row length)
   int col_ctas_per_sm      = 4;   // B2R_COL_CPS   column-partial CTAs per SM (one resident wave)
+  int col_gy_round         = 1;   // B2R_COL_GY_ROUND row ranges of the column-partial plan 1: rounded down to whole waves, 2: up
   int split_ctas_per_sm    = 4;   // B2R_SPLIT_CPS
   int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
@@ -133,6 +134,7 @@ struct Tuning {
   int col_tma              = 1;     // B2R_COL_TMA    1: TMA-staged tiles for narrow contiguous column reductions, 2: off
   int col_tma_tile_kb      = 32;    // B2R_COL_TMA_KB tile size of the TMA ring, KiB
   int col_tma2d_min_mb     = 256;   // B2R_COL_TMA2D_MB smallest matrix (MiB) for the tiled-TMA kernel of wide matrices
+  int col_tma2d_max_row_kb = 16;    // B2R_COL_TMA2D_ROW_KB longest row (KiB) for it: beyond, whole waves of the register-staged kernel are faster
   int tma_stages           = 4;     // B2R_TMA_STAGES stages of the TMA ring (2..8)
   int row_tma              = 0;     // B2R_ROW_TMA    ring kernel for short contiguous rows: unset = by shape, 1: wherever it fits, 2: never
   int row_ring_min_vec     = 8;     // B2R_ROW_RING_MINVEC shortest row (16-byte vectors) that takes the ring kernel by itself
@@ -173,6 +175,7 @@ inline Tuning read_tuning_from_env()
   x.row_chunk_threshold  = env_int("B2R_ROW_CHUNK", x.row_chunk_threshold);
   x.row_cpl              = env_int("B2R_ROW_CPL", x.row_cpl);
   x.col_ctas_per_sm      = env_int("B2R_COL_CPS", x.col_ctas_per_sm);
+  x.col_gy_round         = env_int("B2R_COL_GY_ROUND", x.col_gy_round);
   x.split_ctas_per_sm    = env_int("B2R_SPLIT_CPS", x.split_ctas_per_sm);
   x.key_block_rows       = env_int("B2R_KEY_BLOCK", x.key_block_rows);
   x.key_window_rows      = env_int("B2R_KEY_WINDOW", x.key_window_rows);
@@ -190,6 +193,7 @@ inline Tuning read_tuning_from_env()
   x.col_tma              = env_int("B2R_COL_TMA", x.col_tma);
   x.col_tma_tile_kb      = env_int("B2R_COL_TMA_KB", x.col_tma_tile_kb);
   x.col_tma2d_min_mb     = env_int("B2R_COL_TMA2D_MB", x.col_tma2d_min_mb);
+  x.col_tma2d_max_row_kb = env_int("B2R_COL_TMA2D_ROW_KB", x.col_tma2d_max_row_kb);
   x.tma_stages           = env_int("B2R_TMA_STAGES", x.tma_stages);
   if (x.tma_stages < 2) x.tma_stages = 2;
   if (x.tma_stages > 8) x.tma_stages = 8;
@@ -797,8 +801,11 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
   p.TX              = int(tx);
   p.TY              = TPB / p.TX;
   p.grid_x          = unsigned(ceil_div<int64_t>(ncv, p.TX));
+  // whole waves: column blocks x row ranges must not end just past a multiple of the resident CTAs (rounding the
+  // row ranges up did: 8192 x 8192 fp32 got 640 CTAs for 592 slots, two waves for the work of one)
   const int64_t target = int64_t(sm_count()) * tuning().col_ctas_per_sm;
-  int64_t gy           = ceil_div<int64_t>(target, p.grid_x);
+  int64_t gy           = tuning().col_gy_round == 2 ? ceil_div<int64_t>(target, p.grid_x) : target / p.grid_x;
+  if (gy < 1) gy = 1;
   const int64_t max_gy = ceil_div<int64_t>(n_rows, int64_t(p.TY) * U);  // >= one full unrolled step each
   if (gy > max_gy) gy = max_gy;
   if (gy > 65535) gy = 65535;
@@ -866,7 +873,8 @@ inline ColPlan plan_col_reduce(const InT* data, int64_t n_rows, int64_t n_cols, 
     const int64_t BX = int64_t(32) * V16;
     if (!p.tma && tuning().col_tma == 1 && vec_ok && V16 > 1 && n_cols > BX && n_rows >= 4096 &&
         n_rows < (int64_t(1) << 31) && n_cols < (int64_t(1) << 31) && (size_t(ld) * sizeof(InT)) % 16 == 0 &&
-        size_t(n_rows) * size_t(n_cols) * sizeof(InT) >= (size_t(tuning().col_tma2d_min_mb) << 20)) {
+        size_t(n_rows) * size_t(n_cols) * sizeof(InT) >= (size_t(tuning().col_tma2d_min_mb) << 20) &&
+        row_bytes <= (size_t(tuning().col_tma2d_max_row_kb) << 10)) {
       const int64_t gx  = ceil_div<int64_t>(n_cols, BX);
       const int sms     = sm_count();
       int64_t best_gy = 0, best_cost = 0;
