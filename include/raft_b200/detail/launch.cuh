@@ -117,7 +117,8 @@ struct Tuning {
   int row_cpl              = 0;   // B2R_ROW_CPL   chunks of a row per lane and pass: 1, 2, 4 (0: by row length)
   int col_ctas_per_sm      = 4;   // B2R_COL_CPS   column-partial CTAs per SM (one resident wave)
   int col_gy_round         = 1;   // B2R_COL_GY_ROUND row ranges of the column-partial plan 1: rounded down to whole waves, 2: up
-  int split_ctas_per_sm    = 4;   // B2R_SPLIT_CPS
+  int split_min_kb         = 0;   // B2R_SPLIT_MIN_KB shortest segment of a split row, KiB (0: 32, 128 for inputs of 400 MB and more)
+  int split_ctas_per_sm    = 0;   // B2R_SPLIT_CPS split-row CTAs per SM aimed for (0: 4, 16 for inputs of 400 MB and more)
   int key_block_rows       = 8192;  // B2R_KEY_BLOCK  rows per sorted block (rows-by-key, table algorithm)
   int key_window_rows      = 0;     // B2R_KEY_WINDOW rows per sort window (rows-by-key, sorted algorithm; 0: auto)
   int key_unit_rows        = 0;     // B2R_KEY_UNIT_ROWS rows of one key a warp sums into one partial row (0: by size, 128..384)
@@ -176,6 +177,7 @@ inline Tuning read_tuning_from_env()
   x.row_cpl              = env_int("B2R_ROW_CPL", x.row_cpl);
   x.col_ctas_per_sm      = env_int("B2R_COL_CPS", x.col_ctas_per_sm);
   x.col_gy_round         = env_int("B2R_COL_GY_ROUND", x.col_gy_round);
+  x.split_min_kb         = env_int("B2R_SPLIT_MIN_KB", x.split_min_kb);
   x.split_ctas_per_sm    = env_int("B2R_SPLIT_CPS", x.split_ctas_per_sm);
   x.key_block_rows       = env_int("B2R_KEY_BLOCK", x.key_block_rows);
   x.key_window_rows      = env_int("B2R_KEY_WINDOW", x.key_window_rows);
@@ -371,8 +373,14 @@ inline size_t row_reduce_scratch_bytes(int64_t n_rows, int64_t row_len, size_t i
   const int64_t row_bytes = row_len * int64_t(in_size);
   int n_seg               = 0;  // 0: warp-per-row kernels
   if (n_rows < int64_t(sms) * 16 && row_bytes >= (int64_t(8) << 10)) {
-    const int64_t want    = ceil_div<int64_t>(int64_t(sms) * tuning().split_ctas_per_sm, n_rows);
-    const int64_t max_seg = row_bytes / (int64_t(32) << 10);
+    // few long segments while the launch and the fold of the partials still count (measured up to 270 MB), four
+    // times as many CTAs with segments of at least 128 KB from 400 MB on (fp32 2000 x 200000: 5.99 -> 6.63 TB/s,
+    // 200 x 2 000 000: 6.18 -> 6.66, 1024 x 131072: 5.08 -> 6.07; 16 x 4 000 000 would lose: 5.5 -> 4.9)
+    const bool large      = n_rows * row_bytes >= (int64_t(400) << 20);
+    const int cps         = tuning().split_ctas_per_sm > 0 ? tuning().split_ctas_per_sm : (large ? 16 : 4);
+    const int min_kb      = tuning().split_min_kb > 0 ? tuning().split_min_kb : (large ? 128 : 32);
+    const int64_t want    = ceil_div<int64_t>(int64_t(sms) * cps, n_rows);
+    const int64_t max_seg = row_bytes / (int64_t(min_kb) << 10);
     n_seg                 = int(want < max_seg ? want : max_seg);
     if (n_seg < 1) n_seg = 1;
   }
