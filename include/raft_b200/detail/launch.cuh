@@ -709,15 +709,15 @@ cudaError_t launch_row_reduce(StoreT* out,
   // CTAs to the SMs as they free up, and a fresh warp issues all its loads at once. Measured against two resident
   // waves of long-lived CTAs that loop over their batches (a warp has no load in flight while it reduces and stores
   // a batch): 1 000 000 x 128 fp32 6.63 -> 6.96 TB/s, 100 000 x 1024 6.52 -> 6.95, 250 000 x 1024 6.95 -> 7.28,
-  // 4 000 000 x 32 6.32 -> 6.70, row argmin 8 388 608 x 64 (ring off) 6.41 -> 6.92; rows of 8192 columns and more
-  // (chunk mode) do not care.
+  // 4 000 000 x 32 6.32 -> 6.70, row argmin 8 388 608 x 64 (ring off) 6.41 -> 6.92. Rows of 8192 columns and more
+  // (chunk mode: a warp streams a whole row) keep two resident waves: they do not care back to back and lose 2 %
+  // on a cold single call (32768 x 32768).
   constexpr int kRowCtasPerSm = 256;
 #define B2R_LAUNCH_ROW(VEC_, MODE_, U_, CPL_)                                                    \
   do {                                                                                           \
     auto kern      = row_reduce_kernel<InT, OutT, IdxT, MainOp, ReduceOp, FinalOp, VEC_, U_, MODE_, TPB, CPL_, StoreT>; \
     static int occ = resident_ctas(kern, TPB, 0);                                                \
-    (void)occ;                                                                                   \
-    int64_t ctas   = int64_t(sms) * (cps_knob > 0 ? cps_knob : kRowCtasPerSm);                  \
+    int64_t ctas   = int64_t(sms) * (cps_knob > 0 ? cps_knob : (MODE_ == kChunks ? 2 * occ : kRowCtasPerSm)); \
     const int64_t most = ceil_div<int64_t>(n_b, TPB / 32);                                       \
     if (ctas > most) ctas = most;                                                                \
     int64_t bpc = ceil_div<int64_t>(n_b, ctas);                                                  \
