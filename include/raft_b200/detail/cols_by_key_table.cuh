@@ -19,12 +19,14 @@
 //    step touches 32 different banks (eight multiples of four from r % 8, plus (g + s) % 4), and after four steps
 //    every lane has seen the four columns of the group.
 //  * Keys travel as one byte per column (cbk_keys8_kernel: key, or the dummy slot `nkeys` for a key outside
-//    [0, nkeys) and for the columns past the end), 240 bytes per box beside it in the stage; a lane fetches the
-//    four keys of a column group with one broadcast load.
-//  * The eight consumer warps share the 32 rows and split the 57 column groups of a box; each has its own table
-//    ((nkeys + 1) x 32 floats), so nothing is shared while streaming. Two elements are handled at a time: both
-//    cells are loaded before either is stored, and if they are the same cell the second add takes the first
-//    sum - the chain of shared-memory latencies per element is halved without a second table.
+//    [0, nkeys) and for the columns past the end) plus one flag per column group that holds a key twice, 240 bytes
+//    per box beside it in the stage; a lane fetches the four keys of a column group with one broadcast load.
+//  * The consumer warps (eight; four above 136 keys, where eight tables no longer leave room for three stages)
+//    share the 32 rows and split the 47 or 57 column groups of a box; each has its own table ((nkeys + 1) x 32
+//    floats), so nothing is shared while streaming. The four columns of a group are added all at once - four
+//    cell loads in flight, four adds, four stores - when their keys differ (the flag; with no flagged group in a
+//    warp's share of the box, 7 boxes of 10 with 128 keys, a copy of the walk without any branch runs), otherwise
+//    two at a time with a same-cell check: if both are the same cell the second add takes the first sum.
 //  * At the end of a row tile the tables are added in warp order in fp64 and written as [row][key] (or as an
 //    fp64 partial when the columns are split over CTAs: cbk_merge_kernel).
 //    fp32 cells see at most kCbkTableMaxAdds additions between two flushes (the planner splits the columns
