@@ -323,9 +323,10 @@ inline cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
 }
 
-// Resident CTAs per SM of a kernel: the reductions launch one or two resident waves of
-// long-lived CTAs and loop inside the kernel (measured on B200: ~15 % faster than many short
-// CTAs; two waves' worth of CTAs balance the tail a little better than exactly one).
+// Resident CTAs per SM of a kernel. The column kernels, the chunk mode of the row kernel and the queue-driven
+// kernels launch one or two resident waves of long-lived CTAs and loop inside the kernel (measured on the
+// register-staged column kernel: ~15 % faster than many short CTAs); the direct row kernels do the opposite (see
+// launch_row_reduce).
 template <typename Kernel>
 inline int resident_ctas(Kernel kern, int tpb, size_t smem)
 {

@@ -166,7 +166,8 @@ __global__ void __launch_bounds__(TPB, (sizeof(OutT) <= 8 && U * CPL <= 8 ? 4 : 
   const int nvec  = row_len / VEC;    // VEC divides row_len on the vector path; VEC==1 otherwise
 
   // A CTA owns a contiguous range of row batches (so that it streams one contiguous piece of
-  // the matrix); its warps interleave inside the range.
+  // the matrix); its warps interleave inside the range. The launcher gives a CTA one batch per warp by default
+  // (many short CTAs), more only in chunk mode or when asked to.
   constexpr int64_t warps_total = TPB / 32;
   const int64_t cta_first       = int64_t(blockIdx.x) * batches_per_cta;
   const int64_t warp_global     = cta_first + (threadIdx.x >> 5);
